@@ -1,0 +1,705 @@
+// Split-KV decode / MTP-verify attention over the paged f16 / q8_0 / q4_0 cache, sm_100a.
+//
+// Work unit = (slot, kv head, key chunk): one CTA of 4 warps walks its chunk in 64-key tiles.
+//   staging   K and V head rows of a tile are fetched by 1-D bulk async copies (TMA unit) into a multi-stage
+//             shared-memory ring, completion counted on mbarriers; rows keep their cache format in shared memory.
+//   QK^T      warp w owns keys 16w..16w+15 of the tile: keys on the MMA M axis, the slot's 6 * q_len query rows on N
+//             (all GQA heads and verify rows share one pass over the KV bytes).  int8 / nibbles are widened to f16
+//             exactly in registers (byte permute + one f16x2 subtract), products accumulate in fp32 on the tensor
+//             cores (mma.sync m16n8k16), the per-32 block scale multiplies the fp32 partial sums.
+//   softmax   online, per row, base 2; the tile maximum is exchanged through shared memory, P goes to shared memory
+//             as f16.
+//   PV        warp w owns output dims 64w..64w+63: V^T tiles on M, rows on N, fp32 accumulators in registers.
+//   partials  each unit writes unnormalised (O, m, l); a merge kernel combines a row's chunks in chunk order, applies
+//             the optional sigmoid gate and normalises (reference formula: dec2_combine_k, src/fast/attn_dec2.cu:430-450).
+// The chunk grid is fixed by absolute key index, and a chunk's arithmetic never depends on the other rows of the call:
+// a row's result is a function of its own keys and of chunk_keys only (row t of a T-row call == the 1-row call).
+//
+// Reference counterpart: dec2_k / attn_decode2 (src/fast/attn_dec2.cu:210-530), fp32 FFMA on sm_60.
+#include "common.cuh"
+
+#include <algorithm>
+#include <cstdlib>
+#include <mutex>
+
+namespace b200 {
+namespace {
+
+constexpr int TILE = 64;              // keys per tile
+constexpr int NWARP = 4, NTHR = NWARP * 32;
+constexpr int QSTR = 576;             // bytes per Q row in shared memory (256 f16 + 64: rows g, g+1 on different bank halves)
+constexpr int PSTR = 144;             // bytes per P row (64 f16 + 16)
+constexpr int SDSTR = 132;            // bytes per V-scale row (64 f16 + 4)
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
+
+template <uint32_t KT> struct traits {
+    static constexpr int HB = head_bytes(KT);                       // bytes of a head row in the cache
+    static constexpr int SROW = KT == B200_KV_F16 ? HB + 16 : HB;   // bytes per key row in shared memory (= 4 mod 32 words)
+    static constexpr int STAGE = 2 * TILE * SROW;                   // K rows then V rows
+    static constexpr bool SCALED = KT != B200_KV_F16;
+};
+
+// M-row (0..7) -> key of the warp's 16-key group, chosen so that the A-fragment loads of a phase hit distinct banks
+template <uint32_t KT> __device__ __forceinline__ int key_perm(int g) {
+    if constexpr (KT == B200_KV_F16) return (g >> 1) + 4 * (g & 1);       // 16-byte loads: lanes of a phase 4 keys apart
+    else if constexpr (KT == B200_KV_Q8_0) return 2 * (g & 3) + (g >> 2); // 8-byte loads: 2 keys apart
+    else return g;
+}
+// position of head dim d inside the shared-memory Q row, so that lane t of a quad reads dims of block b for both
+// k-steps of the block with one 16-byte load at 64 b + 16 t
+template <uint32_t KT> __device__ __forceinline__ int q_slot(int d) {
+    if constexpr (KT == B200_KV_Q4_0) {
+        const int b = d >> 5, i = d & 31;          // nibble order: byte j = dims j | j + 16
+        return b * 32 + ((i & 15) >> 2) * 8 + (i >> 4) * 4 + (i & 3);
+    } else return d;
+}
+
+struct dec_args {
+    const float * q;
+    kv_view g;
+    float * po; float * pm; float * pl;   // partials [unit][R][256], [unit][R], [unit][R]
+    const int32_t * pos;                  // per-row positions (device) or nullptr
+    const int32_t * p0p;                  // device first position or nullptr
+    int p0;
+    int q_len, n_slots, Hq;
+    float qscale;                         // softmax scale * log2(e)
+    int CH, max_chunks;
+    unsigned * status;
+};
+
+__device__ __forceinline__ int row_pos(const dec_args & a, int slot, int j) {
+    const int r = slot * a.q_len + j;
+    if (a.pos) return a.pos[r];
+    return (a.p0p ? *a.p0p : a.p0) + r;
+}
+
+// two int8 (already offset by 128) at bytes (2 * HI, 2 * HI + 1) of u -> f16x2
+template <int HI> __device__ __forceinline__ uint32_t cvt_i8x2(uint32_t u) {
+    return hsub2_u32(__byte_perm(u, 0x64646464u, HI ? 0x7362 : 0x5140), 0x64806480u);
+}
+// bytes holding values 0..15 (+8 bias) at bytes (2 * HI, 2 * HI + 1) -> f16x2 of (value - 8)
+template <int HI> __device__ __forceinline__ uint32_t cvt_n4x2(uint32_t u) {
+    return hsub2_u32(__byte_perm(u, 0x64646464u, HI ? 0x7362 : 0x5140), 0x64086408u);
+}
+
+template <uint32_t KT, int NT>
+__global__ void __launch_bounds__(NTHR) decode_part_k(const dec_args a, const int nstage) {
+    using TR = traits<KT>;
+    constexpr int HB = TR::HB, SROW = TR::SROW;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int chunk = blockIdx.x, hk = blockIdx.y, slot = blockIdx.z;
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, g = lane >> 2, t = lane & 3;
+    const int R = a.q_len * GQA;
+
+    // visible keys of the slot = 1 + the largest row position
+    int n_slot = 0;
+    for (int j = 0; j < a.q_len; ++j) n_slot = max(n_slot, row_pos(a, slot, j) + 1);
+    const int k_lo = chunk * a.CH;
+    if (k_lo >= n_slot) return;
+    const int k_hi = min(k_lo + a.CH, n_slot);
+    const int ntiles = (k_hi - k_lo + TILE - 1) / TILE;
+
+    // shared memory carve-up
+    uint64_t * full = reinterpret_cast<uint64_t *>(smem);                    // [nstage]
+    unsigned char * stg = smem + 128;                                        // nstage * STAGE
+    unsigned char * Qs = stg + (size_t) nstage * TR::STAGE;                  // [NT*8][QSTR]
+    unsigned char * Ps = Qs + NT * 8 * QSTR;                                 // [NT*8][PSTR]
+    unsigned char * Sd = Ps + NT * 8 * PSTR;                                 // [8][SDSTR]  V block scales, transposed
+    float * wmax = reinterpret_cast<float *>(Sd + 8 * SDSTR);                // [NWARP][NT*8]
+    float * wl = wmax + NWARP * NT * 8;                                      // [NWARP][NT*8]
+
+    if (tid == 0) {
+        for (int s = 0; s < nstage; ++s) mbar_init(&full[s], 1);
+        mbar_fence_init();
+    }
+    // Q rows -> shared memory as f16, scaled; row r = j * 6 + hh (verify row j, head hh of the group)
+    for (int i = tid; i < NT * 8 * (DH / 4); i += NTHR) {
+        const int r = i / (DH / 4), d4 = (i - r * (DH / 4)) * 4;
+        float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (r < R) {
+            const int j = r / GQA, hh = r - j * GQA;
+            v = *reinterpret_cast<const float4 *>(a.q + ((size_t) (slot * a.q_len + j) * a.Hq + hk * GQA + hh) * DH + d4);
+        }
+        const float vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            *reinterpret_cast<__half *>(Qs + r * QSTR + q_slot<KT>(d4 + e) * 2) = __float2half_rn(vv[e] * a.qscale);
+    }
+    __syncthreads();
+
+    const int32_t * tab = a.g.pt ? a.g.pt + (a.g.rtab ? a.g.rtab[slot * a.q_len] : 0) : nullptr;
+    const unsigned long long hoff = (unsigned long long) hk * HB;
+
+    // producer: warp 0 copies the 64 K rows and 64 V rows of tile `it` into stage it % nstage (rows past the slot's
+    // last key are replaced by that last key: always readable, and masked in the softmax)
+    auto issue = [&](int it) {
+        const int s = it % nstage;
+        unsigned char * dst = stg + (size_t) s * TR::STAGE;
+        if (lane == 0) mbar_expect_tx(&full[s], 2u * TILE * HB);
+        __syncwarp();
+#pragma unroll
+        for (int rr = 0; rr < TILE / 32; ++rr) {
+            const int row = lane + 32 * rr;
+            const int p = min(k_lo + it * TILE + row, n_slot - 1);
+            unsigned long long off;
+            if (tab) {
+                const int pg = tab[p >> a.g.psh];
+                if (pg < 0) { atomicOr(a.status, ST_BAD_PAGE); off = 0; }
+                else off = (unsigned long long) pg * a.g.pstride + (unsigned long long) (p & ((1 << a.g.psh) - 1)) * a.g.rowb;
+            } else off = (unsigned long long) p * a.g.rowb;
+            off += hoff;
+            bulk_g2s(dst + row * SROW, a.g.k + off, HB, &full[s]);
+            bulk_g2s(dst + (TILE + row) * SROW, a.g.v + off, HB, &full[s]);
+        }
+    };
+    if (w == 0)
+        for (int it = 0; it < nstage && it < ntiles; ++it) issue(it);
+
+    // per-lane row bookkeeping: this lane's score / output columns are rows 8i + 2t and 8i + 2t + 1
+    int rpos[NT][2];
+    float m_run[NT][2], l_run[NT][2];
+#pragma unroll
+    for (int i = 0; i < NT; ++i)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int r = 8 * i + 2 * t + e;
+            rpos[i][e] = r < R ? row_pos(a, slot, r / GQA) : -1;
+            m_run[i][e] = B200_NEG_INF;
+            l_run[i][e] = 0.0f;
+        }
+    float O[4][NT][4];
+#pragma unroll
+    for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+        for (int i = 0; i < NT; ++i)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) O[mt][i][e] = 0.0f;
+
+    const int kA = 16 * w + key_perm<KT>(g), kB = kA + 8;   // this lane's two keys (tile-relative) in the QK phase
+
+    for (int it = 0; it < ntiles; ++it) {
+        const int s = it % nstage;
+        const unsigned char * Ks = stg + (size_t) s * TR::STAGE;
+        const unsigned char * Vs = Ks + TILE * SROW;
+        mbar_wait(&full[s], (uint32_t) ((it / nstage) & 1), a.status);
+
+        // ---------------- S = K Q^T for the warp's 16 keys ----------------
+        float S[NT][4];
+#pragma unroll
+        for (int i = 0; i < NT; ++i) { S[i][0] = S[i][1] = S[i][2] = S[i][3] = 0.0f; }
+        const unsigned char * rowA = Ks + kA * SROW, * rowB = Ks + kB * SROW;
+        if constexpr (KT == B200_KV_F16) {
+#pragma unroll
+            for (int b = 0; b < NBLK; ++b) {
+                const uint4 wa = *reinterpret_cast<const uint4 *>(rowA + 64 * b + 16 * t);
+                const uint4 wb = *reinterpret_cast<const uint4 *>(rowB + 64 * b + 16 * t);
+                const uint32_t a0[4] = {wa.x, wb.x, wa.y, wb.y}, a1[4] = {wa.z, wb.z, wa.w, wb.w};
+#pragma unroll
+                for (int i = 0; i < NT; ++i) {
+                    const uint4 qv = *reinterpret_cast<const uint4 *>(Qs + (8 * i + g) * QSTR + 64 * b + 16 * t);
+                    mma16816(S[i], a0, qv.x, qv.y);
+                    mma16816(S[i], a1, qv.z, qv.w);
+                }
+            }
+        } else {
+            uint4 sA, sB;   // the 8 block scales of each key (q8_0); q4_0 reads them block by block
+            if constexpr (KT == B200_KV_Q8_0) {
+                sA = *reinterpret_cast<const uint4 *>(rowA);
+                sB = *reinterpret_cast<const uint4 *>(rowB);
+            }
+#pragma unroll
+            for (int b = 0; b < NBLK; ++b) {
+                uint32_t a0[4], a1[4];
+                float dA, dB;
+                if constexpr (KT == B200_KV_Q8_0) {
+                    const uint2 wa = *reinterpret_cast<const uint2 *>(rowA + 16 + 32 * b + 8 * t);
+                    const uint2 wb = *reinterpret_cast<const uint2 *>(rowB + 16 + 32 * b + 8 * t);
+                    const uint32_t ax = wa.x ^ 0x80808080u, ay = wa.y ^ 0x80808080u;
+                    const uint32_t bx = wb.x ^ 0x80808080u, by = wb.y ^ 0x80808080u;
+                    a0[0] = cvt_i8x2<0>(ax); a0[1] = cvt_i8x2<0>(bx); a0[2] = cvt_i8x2<1>(ax); a0[3] = cvt_i8x2<1>(bx);
+                    a1[0] = cvt_i8x2<0>(ay); a1[1] = cvt_i8x2<0>(by); a1[2] = cvt_i8x2<1>(ay); a1[3] = cvt_i8x2<1>(by);
+                    const uint32_t swA = (&sA.x)[b >> 1], swB = (&sB.x)[b >> 1];
+                    dA = __half2float(__ushort_as_half((unsigned short) ((b & 1) ? swA >> 16 : swA & 0xffffu)));
+                    dB = __half2float(__ushort_as_half((unsigned short) ((b & 1) ? swB >> 16 : swB & 0xffffu)));
+                } else {
+                    // block at byte 18 b: f16 d, then 16 bytes; this lane takes bytes 4t..4t+3 (dims 4t.. low nibbles,
+                    // 16+4t.. high nibbles).  The 16 bytes start on a 2-byte boundary for even b.
+                    uint32_t qa, qb;
+                    if ((b & 1) == 0) {
+                        const uint32_t * pa = reinterpret_cast<const uint32_t *>(rowA + 18 * b + 4 * t);
+                        const uint32_t * pb = reinterpret_cast<const uint32_t *>(rowB + 18 * b + 4 * t);
+                        qa = __funnelshift_r(pa[0], pa[1], 16);
+                        qb = __funnelshift_r(pb[0], pb[1], 16);
+                    } else {
+                        qa = *reinterpret_cast<const uint32_t *>(rowA + 18 * b + 2 + 4 * t);
+                        qb = *reinterpret_cast<const uint32_t *>(rowB + 18 * b + 2 + 4 * t);
+                    }
+                    const uint32_t al = qa & 0x0f0f0f0fu, ah = (qa >> 4) & 0x0f0f0f0fu;
+                    const uint32_t bl = qb & 0x0f0f0f0fu, bh = (qb >> 4) & 0x0f0f0f0fu;
+                    a0[0] = cvt_n4x2<0>(al); a0[1] = cvt_n4x2<0>(bl); a0[2] = cvt_n4x2<1>(al); a0[3] = cvt_n4x2<1>(bl);
+                    a1[0] = cvt_n4x2<0>(ah); a1[1] = cvt_n4x2<0>(bh); a1[2] = cvt_n4x2<1>(ah); a1[3] = cvt_n4x2<1>(bh);
+                    dA = __half2float(*reinterpret_cast<const __half *>(rowA + 18 * b));
+                    dB = __half2float(*reinterpret_cast<const __half *>(rowB + 18 * b));
+                }
+#pragma unroll
+                for (int i = 0; i < NT; ++i) {
+                    const uint4 qv = *reinterpret_cast<const uint4 *>(Qs + (8 * i + g) * QSTR + 64 * b + 16 * t);
+                    float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                    mma16816(c, a0, qv.x, qv.y);
+                    mma16816(c, a1, qv.z, qv.w);
+                    S[i][0] = fmaf(dA, c[0], S[i][0]); S[i][1] = fmaf(dA, c[1], S[i][1]);
+                    S[i][2] = fmaf(dB, c[2], S[i][2]); S[i][3] = fmaf(dB, c[3], S[i][3]);
+                }
+            }
+        }
+        // causal / chunk mask, warp-level row maxima
+        const int keyA = k_lo + it * TILE + kA, keyB = keyA + 8;
+#pragma unroll
+        for (int i = 0; i < NT; ++i)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                if (keyA > rpos[i][e] || keyA >= k_hi) S[i][e] = B200_NEG_INF;
+                if (keyB > rpos[i][e] || keyB >= k_hi) S[i][2 + e] = B200_NEG_INF;
+                float mx = fmaxf(S[i][e], S[i][2 + e]);
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+                if (g == 0) wmax[w * NT * 8 + 8 * i + 2 * t + e] = mx;
+            }
+        __syncthreads();   // B1: row maxima visible; every warp is done with the previous tile's PV
+        if (w == 0 && it >= 1 && it - 1 + nstage < ntiles) issue(it - 1 + nstage);
+
+        // ---------------- online softmax, P -> shared memory ----------------
+        float fsc[NT][2];
+#pragma unroll
+        for (int i = 0; i < NT; ++i)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int r = 8 * i + 2 * t + e;
+                float mx = fmaxf(fmaxf(wmax[r], wmax[NT * 8 + r]), fmaxf(wmax[2 * NT * 8 + r], wmax[3 * NT * 8 + r]));
+                const float mnew = fmaxf(m_run[i][e], mx);
+                const float msafe = mnew == B200_NEG_INF ? 0.0f : mnew;
+                fsc[i][e] = ex2f(m_run[i][e] - msafe);
+                m_run[i][e] = mnew;
+                const __half pa = __float2half_rn(S[i][e] == B200_NEG_INF ? 0.0f : ex2f(S[i][e] - msafe));
+                const __half pb = __float2half_rn(S[i][2 + e] == B200_NEG_INF ? 0.0f : ex2f(S[i][2 + e] - msafe));
+                l_run[i][e] = fmaf(l_run[i][e], fsc[i][e], __half2float(pa) + __half2float(pb));
+                *reinterpret_cast<__half *>(Ps + r * PSTR + kA * 2) = pa;
+                *reinterpret_cast<__half *>(Ps + r * PSTR + kB * 2) = pb;
+            }
+        if constexpr (TR::SCALED) {   // V block scales, transposed to [block][key]
+            const int key = tid >> 1, b0 = (tid & 1) * 4;
+#pragma unroll
+            for (int b = b0; b < b0 + 4; ++b) {
+                const unsigned char * src = KT == B200_KV_Q8_0 ? Vs + key * SROW + 2 * b : Vs + key * SROW + 18 * b;
+                *reinterpret_cast<uint16_t *>(Sd + b * SDSTR + key * 2) = *reinterpret_cast<const uint16_t *>(src);
+            }
+        }
+        // rescale the running output
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+            for (int i = 0; i < NT; ++i) {
+                O[mt][i][0] *= fsc[i][0]; O[mt][i][1] *= fsc[i][1];
+                O[mt][i][2] *= fsc[i][0]; O[mt][i][3] *= fsc[i][1];
+            }
+        __syncthreads();   // B2: P and the V scales are visible
+
+        // ---------------- O^T += V^T P^T for the warp's 64 output dims ----------------
+#pragma unroll
+        for (int u = 0; u < TILE / 16; ++u) {
+            uint32_t pw[NT][2];
+#pragma unroll
+            for (int i = 0; i < NT; ++i) {
+                pw[i][0] = *reinterpret_cast<const uint32_t *>(Ps + (8 * i + g) * PSTR + (16 * u + 2 * t) * 2);
+                pw[i][1] = *reinterpret_cast<const uint32_t *>(Ps + (8 * i + g) * PSTR + (16 * u + 2 * t + 8) * 2);
+            }
+            if constexpr (KT == B200_KV_F16) {
+#pragma unroll
+                for (int mt = 0; mt < 4; ++mt) {
+                    // four 8x8 tiles, transposed on load: (keys 0-7 | 8-15) x (dims 0-7 | 8-15) of this m-tile
+                    const int mj = lane >> 3, mr = lane & 7;
+                    const unsigned char * p = Vs + (16 * u + (mj >> 1) * 8 + mr) * SROW + (64 * w + 16 * mt + (mj & 1) * 8) * 2;
+                    uint32_t av[4];
+                    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(av[0]), "=r"(av[1]), "=r"(av[2]), "=r"(av[3]) : "r"(smem_u32(p)));
+#pragma unroll
+                    for (int i = 0; i < NT; ++i) mma16816(O[mt][i], av, pw[i][0], pw[i][1]);
+                }
+            } else {
+                const unsigned char * v0 = Vs + (16 * u + 2 * t) * SROW, * v1 = v0 + SROW, * v2 = v0 + 8 * SROW, * v3 = v2 + SROW;
+#pragma unroll
+                for (int y = 0; y < 2; ++y) {
+                    const int blk = 2 * w + y;
+                    uint32_t ax[4], ay[4];   // m-tiles X and Y of this block
+                    if constexpr (KT == B200_KV_Q8_0) {
+                        const int col = 16 + 32 * blk + 4 * g;
+                        const uint32_t w0 = *reinterpret_cast<const uint32_t *>(v0 + col) ^ 0x80808080u;
+                        const uint32_t w1 = *reinterpret_cast<const uint32_t *>(v1 + col) ^ 0x80808080u;
+                        const uint32_t w2 = *reinterpret_cast<const uint32_t *>(v2 + col) ^ 0x80808080u;
+                        const uint32_t w3 = *reinterpret_cast<const uint32_t *>(v3 + col) ^ 0x80808080u;
+                        // interleave key pairs: e01 = (k0.d0, k1.d0, k0.d1, k1.d1), f01 = (k0.d2, k1.d2, k0.d3, k1.d3)
+                        const uint32_t e01 = __byte_perm(w0, w1, 0x5140), f01 = __byte_perm(w0, w1, 0x7362);
+                        const uint32_t e23 = __byte_perm(w2, w3, 0x5140), f23 = __byte_perm(w2, w3, 0x7362);
+                        ax[0] = cvt_i8x2<0>(e01); ax[1] = cvt_i8x2<1>(e01); ax[2] = cvt_i8x2<0>(e23); ax[3] = cvt_i8x2<1>(e23);
+                        ay[0] = cvt_i8x2<0>(f01); ay[1] = cvt_i8x2<1>(f01); ay[2] = cvt_i8x2<0>(f23); ay[3] = cvt_i8x2<1>(f23);
+                    } else {
+                        const int col = 18 * blk + 2 + 2 * g;   // bytes 2g, 2g+1 of the block: dims 2g, 2g+1 | 16+2g, 17+2g
+                        const uint32_t h0 = *reinterpret_cast<const uint16_t *>(v0 + col), h1 = *reinterpret_cast<const uint16_t *>(v1 + col);
+                        const uint32_t h2 = *reinterpret_cast<const uint16_t *>(v2 + col), h3 = *reinterpret_cast<const uint16_t *>(v3 + col);
+                        const uint32_t w01 = h0 | (h1 << 16), w23 = h2 | (h3 << 16);   // bytes (k0.B0, k0.B1, k1.B0, k1.B1)
+                        const uint32_t l01 = w01 & 0x0f0f0f0fu, u01 = (w01 >> 4) & 0x0f0f0f0fu;
+                        const uint32_t l23 = w23 & 0x0f0f0f0fu, u23 = (w23 >> 4) & 0x0f0f0f0fu;
+                        // (k0.x, k1.x) pairs: bytes 0 and 2 -> dim 2g (+16), bytes 1 and 3 -> dim 2g+1 (+16)
+                        ax[0] = hsub2_u32(__byte_perm(l01, 0x64646464u, 0x6240), 0x64086408u);
+                        ax[1] = hsub2_u32(__byte_perm(l01, 0x64646464u, 0x7351), 0x64086408u);
+                        ax[2] = hsub2_u32(__byte_perm(l23, 0x64646464u, 0x6240), 0x64086408u);
+                        ax[3] = hsub2_u32(__byte_perm(l23, 0x64646464u, 0x7351), 0x64086408u);
+                        ay[0] = hsub2_u32(__byte_perm(u01, 0x64646464u, 0x6240), 0x64086408u);
+                        ay[1] = hsub2_u32(__byte_perm(u01, 0x64646464u, 0x7351), 0x64086408u);
+                        ay[2] = hsub2_u32(__byte_perm(u23, 0x64646464u, 0x6240), 0x64086408u);
+                        ay[3] = hsub2_u32(__byte_perm(u23, 0x64646464u, 0x7351), 0x64086408u);
+                    }
+                    const uint32_t sd0 = *reinterpret_cast<const uint32_t *>(Sd + blk * SDSTR + (16 * u + 2 * t) * 2);
+                    const uint32_t sd1 = *reinterpret_cast<const uint32_t *>(Sd + blk * SDSTR + (16 * u + 2 * t + 8) * 2);
+#pragma unroll
+                    for (int i = 0; i < NT; ++i) {
+                        const uint32_t b0 = hmul2_u32(pw[i][0], sd0), b1 = hmul2_u32(pw[i][1], sd1);
+                        mma16816(O[2 * y][i], ax, b0, b1);
+                        mma16816(O[2 * y + 1][i], ay, b0, b1);
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------- write the unit's partial ----------------
+    // l: sum over the lanes that share this row pair (same t), then over the warps
+#pragma unroll
+    for (int i = 0; i < NT; ++i)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            float l = l_run[i][e];
+            l += __shfl_xor_sync(0xffffffffu, l, 4);
+            l += __shfl_xor_sync(0xffffffffu, l, 8);
+            l += __shfl_xor_sync(0xffffffffu, l, 16);
+            if (g == 0) wl[w * NT * 8 + 8 * i + 2 * t + e] = l;
+        }
+    __syncthreads();
+    const size_t unit = ((size_t) slot * a.g.Hkv + hk) * a.max_chunks + chunk;
+    if (w == 0 && g == 0) {
+#pragma unroll
+        for (int i = 0; i < NT; ++i)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int r = 8 * i + 2 * t + e;
+                if (r < R) {
+                    a.pm[unit * R + r] = m_run[i][e];
+                    a.pl[unit * R + r] = (wl[r] + wl[NT * 8 + r]) + (wl[2 * NT * 8 + r] + wl[3 * NT * 8 + r]);
+                }
+            }
+    }
+#pragma unroll
+    for (int i = 0; i < NT; ++i)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int r = 8 * i + 2 * t + e;
+            if (r >= R) continue;
+            float * dst = a.po + (unit * R + r) * DH;
+            if constexpr (KT == B200_KV_F16) {
+#pragma unroll
+                for (int mt = 0; mt < 4; ++mt) {
+                    dst[64 * w + 16 * mt + g] = O[mt][i][e];
+                    dst[64 * w + 16 * mt + g + 8] = O[mt][i][2 + e];
+                }
+            } else if constexpr (KT == B200_KV_Q8_0) {
+#pragma unroll
+                for (int y = 0; y < 2; ++y)
+                    *reinterpret_cast<float4 *>(dst + 64 * w + 32 * y + 4 * g) =
+                        make_float4(O[2 * y][i][e], O[2 * y][i][2 + e], O[2 * y + 1][i][e], O[2 * y + 1][i][2 + e]);
+            } else {
+#pragma unroll
+                for (int y = 0; y < 2; ++y) {
+                    *reinterpret_cast<float2 *>(dst + 64 * w + 32 * y + 2 * g) = make_float2(O[2 * y][i][e], O[2 * y][i][2 + e]);
+                    *reinterpret_cast<float2 *>(dst + 64 * w + 32 * y + 16 + 2 * g) = make_float2(O[2 * y + 1][i][e], O[2 * y + 1][i][2 + e]);
+                }
+            }
+        }
+}
+
+// Merge a row's chunk partials in chunk order.  grid (rows, Hq), 64 threads (one float4 of the head each).
+//   out != nullptr : out = num / den (* sigmoid(gate)); rows that saw no key give zeros
+//   fo  != nullptr : unnormalised num, max in natural-log units, den (for a cross-GPU merge)
+__global__ void __launch_bounds__(64) decode_merge_k(const dec_args a, const float * __restrict__ gate, float * __restrict__ out,
+                                                     float * __restrict__ fo, float * __restrict__ fm, float * __restrict__ fl) {
+    const int h = blockIdx.y, row = blockIdx.x, slot = row / a.q_len, j = row - slot * a.q_len;
+    const int hk = h / GQA, hh = h - hk * GQA, r = j * GQA + hh, R = a.q_len * GQA;
+    const int pos = row_pos(a, slot, j);
+    const int nch = pos < 0 ? 0 : pos / a.CH + 1;
+    const size_t unit0 = ((size_t) slot * a.g.Hkv + hk) * a.max_chunks;
+    float M = B200_NEG_INF;
+    for (int c = 0; c < nch; ++c) M = fmaxf(M, a.pm[(unit0 + c) * R + r]);
+    float den = 0.0f;
+    float4 num = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int c = 0; c < nch; ++c) {
+        const float ms = a.pm[(unit0 + c) * R + r];
+        if (ms == B200_NEG_INF) continue;
+        const float f = ex2f(ms - M);
+        den = fmaf(f, a.pl[(unit0 + c) * R + r], den);
+        const float4 o = reinterpret_cast<const float4 *>(a.po + ((unit0 + c) * R + r) * DH)[threadIdx.x];
+        num.x = fmaf(f, o.x, num.x); num.y = fmaf(f, o.y, num.y); num.z = fmaf(f, o.z, num.z); num.w = fmaf(f, o.w, num.w);
+    }
+    const size_t oi = ((size_t) row * a.Hq + h) * (DH / 4) + threadIdx.x;
+    if (fo) {
+        reinterpret_cast<float4 *>(fo)[oi] = num;
+        if (threadIdx.x == 0) { fm[(size_t) row * a.Hq + h] = M * LN2; fl[(size_t) row * a.Hq + h] = den; }
+    }
+    if (out) {
+        float4 y = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (den > 0.0f) {
+            const float inv = 1.0f / den;
+            y = make_float4(num.x * inv, num.y * inv, num.z * inv, num.w * inv);
+            if (gate) {
+                const float4 gv = reinterpret_cast<const float4 *>(gate)[oi];
+                y.x *= 1.0f / (1.0f + expf(-gv.x)); y.y *= 1.0f / (1.0f + expf(-gv.y));
+                y.z *= 1.0f / (1.0f + expf(-gv.z)); y.w *= 1.0f / (1.0f + expf(-gv.w));
+            }
+        }
+        reinterpret_cast<float4 *>(out)[oi] = y;
+    }
+}
+
+// Merge of caller-provided partials (cross-GPU sequence split): part_o [nparts][R][D], part_m (natural log) / part_l
+// [nparts][R]; one block per row, D/4 threads.
+__global__ void merge_parts_k(const float * __restrict__ po, const float * __restrict__ pm, const float * __restrict__ pl,
+                              int nparts, int R, int D, const float * __restrict__ gate, float * __restrict__ out) {
+    const int r = blockIdx.x, i = threadIdx.x;
+    float M = B200_NEG_INF;
+    for (int s = 0; s < nparts; ++s) M = fmaxf(M, pm[(size_t) s * R + r]);
+    float den = 0.0f;
+    float4 num = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int s = 0; s < nparts; ++s) {
+        const float ms = pm[(size_t) s * R + r];
+        if (ms == B200_NEG_INF) continue;
+        const float f = ex2f((ms - M) * LOG2E);
+        den = fmaf(f, pl[(size_t) s * R + r], den);
+        const float4 o = reinterpret_cast<const float4 *>(po + ((size_t) s * R + r) * D)[i];
+        num.x = fmaf(f, o.x, num.x); num.y = fmaf(f, o.y, num.y); num.z = fmaf(f, o.z, num.z); num.w = fmaf(f, o.w, num.w);
+    }
+    float4 y = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (den > 0.0f) {
+        const float inv = 1.0f / den;
+        y = make_float4(num.x * inv, num.y * inv, num.z * inv, num.w * inv);
+        if (gate) {
+            const float4 gv = reinterpret_cast<const float4 *>(gate + (size_t) r * D)[i];
+            y.x *= 1.0f / (1.0f + expf(-gv.x)); y.y *= 1.0f / (1.0f + expf(-gv.y));
+            y.z *= 1.0f / (1.0f + expf(-gv.z)); y.w *= 1.0f / (1.0f + expf(-gv.w));
+        }
+    }
+    reinterpret_cast<float4 *>(out + (size_t) r * D)[i] = y;
+}
+
+// ------------------------------------------------------------------------------------------------ host side ----
+constexpr int DEFAULT_CHUNK = 512;
+int g_chunk = 0;            // 0 = not read yet
+int g_chunk_override = 0;   // set_nsplit
+
+int env_chunk() {
+    const char * e = getenv("B200ATTN_CHUNK");
+    int v = e && *e ? atoi(e) : DEFAULT_CHUNK;
+    if (v < TILE) v = TILE;
+    return (v + TILE - 1) / TILE * TILE;
+}
+int default_chunk() {
+    if (!g_chunk) g_chunk = env_chunk();
+    return g_chunk;
+}
+
+// split partials per (device, stream): grown on demand, never shrunk, so the pointers stay valid for captured graphs
+// once a call of the largest size has run eagerly (same ownership rule as the reference, src/fast/attn_dec2.cu:452-464)
+struct scratch { int dev = -1; cudaStream_t s = nullptr; float * p = nullptr; size_t cap = 0; };
+scratch g_scr[64];
+int g_nscr = 0;
+std::mutex g_mu;
+
+float * scratch_for(cudaStream_t s, size_t floats) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lk(g_mu);
+    scratch * e = nullptr;
+    for (int i = 0; i < g_nscr; ++i) if (g_scr[i].dev == dev && g_scr[i].s == s) e = &g_scr[i];
+    if (!e) {
+        if (g_nscr == 64) return nullptr;
+        e = &g_scr[g_nscr++];
+        e->dev = dev; e->s = s;
+    }
+    if (floats > e->cap) {
+        if (e->p) { cudaStreamSynchronize(s); cudaFree(e->p); e->p = nullptr; e->cap = 0; }
+        const size_t want = std::max(floats, (size_t) 1 << 20);
+        if (cudaMalloc(&e->p, want * sizeof(float)) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+        e->cap = want;
+    }
+    return e->p;
+}
+
+template <uint32_t KT, int NT> size_t smem_bytes(int nstage) {
+    return 128 + (size_t) nstage * traits<KT>::STAGE + NT * 8 * (QSTR + PSTR) + 8 * SDSTR + 2 * NWARP * NT * 8 * sizeof(float);
+}
+
+template <uint32_t KT, int NT>
+int launch_part(const dec_args & a, dim3 grid, cudaStream_t s) {
+    // deepest ring that still lets two CTAs share an SM (227 KB usable), at least 2 stages
+    int nstage = 4;
+    while (nstage > 2 && 2 * (smem_bytes<KT, NT>(nstage) + 1024) > 227 * 1024) --nstage;
+    const size_t sm = smem_bytes<KT, NT>(nstage);
+    static bool attr_done[64] = {};   // per instantiation and device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_done[dev & 63]) {
+        if (cudaFuncSetAttribute(decode_part_k<KT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) sm) != cudaSuccess)
+            return launch_status("attn_decode (shared memory attribute)");
+        attr_done[dev & 63] = true;
+    }
+    decode_part_k<KT, NT><<<grid, NTHR, sm, s>>>(a, nstage);
+    return B200_OK;
+}
+
+template <uint32_t KT>
+int launch_part_nt(const dec_args & a, dim3 grid, cudaStream_t s) {
+    const int nt = (a.q_len * GQA + 7) / 8;
+    return nt == 1 ? launch_part<KT, 1>(a, grid, s) : nt == 2 ? launch_part<KT, 2>(a, grid, s) : launch_part<KT, 3>(a, grid, s);
+}
+
+int auto_chunk(long long total_keys, int Hkv) {
+    // enough units for ~4 waves over the SMs at two CTAs each, chunks between 256 and 4096 keys
+    int sms = 148;
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long units = 8LL * sms;
+    long long ch = total_keys * Hkv / units;
+    int c = 256;
+    while (c < 4096 && c < ch) c *= 2;
+    return c;
+}
+
+}  // namespace
+
+// q [rows][Hq][256]; rows = n_slots * q_len. Exactly one of (pos), (p0p), (p0) gives the positions.
+int decode_impl(const float * q, const b200_kv_cache * c, float * out, const float * gate, float * fo, float * fm, float * fl,
+                int n_slots, int q_len, const int32_t * pos, const int32_t * p0p, int p0, int max_n, int Hq, float scale,
+                int chunk_keys, cudaStream_t s, const char * who) {
+    if (!c || !q || !c->k || !c->v) B200_REFUSE(B200_ERR_SHAPE, "%s: null argument", who);
+    if (c->D != DH || Hq != GQA * c->Hkv || c->Hkv <= 0) B200_REFUSE(B200_ERR_SHAPE, "%s: unsupported shape (D=%d Hq=%d Hkv=%d)", who, c->D, Hq, c->Hkv);
+    if (c->type != B200_KV_F16 && c->type != B200_KV_Q8_0 && c->type != B200_KV_Q4_0) B200_REFUSE(B200_ERR_SHAPE, "%s: unsupported cache type %u", who, c->type);
+    if (n_slots < 1 || q_len < 1 || q_len > B200_MAX_QLEN) B200_REFUSE(B200_ERR_SHAPE, "%s: unsupported rows (slots=%d q_len=%d)", who, n_slots, q_len);
+    if (n_slots > 65535) B200_REFUSE(B200_ERR_SHAPE, "%s: more than 65535 slots", who);
+    if (!aligned16(c->k) || !aligned16(c->v) || !aligned16(q) || (out && !aligned16(out)) || (gate && !aligned16(gate)) ||
+        (c->pt && c->pstride % 16))
+        B200_REFUSE(B200_ERR_SHAPE, "%s: cache base, page stride, q, out and gate must be 16-byte aligned", who);
+    if (c->pt && (c->psh < 0 || c->psh > 30)) B200_REFUSE(B200_ERR_SHAPE, "%s: bad page shift %d", who, c->psh);
+    if (max_n < 1) max_n = 1;
+    int CH = chunk_keys > 0 ? (chunk_keys + TILE - 1) / TILE * TILE : chunk_keys < 0 ? auto_chunk((long long) n_slots * max_n / 2, c->Hkv)
+                                                                                  : (g_chunk_override > 0 ? g_chunk_override : default_chunk());
+    const int max_chunks = (max_n + CH - 1) / CH;
+    if (max_chunks > 65535 * 32) B200_REFUSE(B200_ERR_SHAPE, "%s: too many chunks", who);
+    const int R = q_len * GQA;
+    const size_t units = (size_t) n_slots * c->Hkv * max_chunks;
+    float * scr = scratch_for(s, units * R * (DH + 2));
+    if (!scr) B200_REFUSE(B200_ERR_ALLOC, "%s: split scratch (%zu floats) could not be allocated", who, units * R * (DH + 2));
+    unsigned * st = device_status_word();
+    if (!st) return B200_ERR_CUDA;
+    dec_args a;
+    a.q = q; a.g = view_of(*c);
+    a.po = scr; a.pm = scr + units * R * DH; a.pl = a.pm + units * R;
+    a.pos = pos; a.p0p = p0p; a.p0 = p0;
+    a.q_len = q_len; a.n_slots = n_slots; a.Hq = Hq;
+    a.qscale = scale * LOG2E;
+    a.CH = CH; a.max_chunks = max_chunks; a.status = st;
+    const dim3 grid(max_chunks, c->Hkv, n_slots);
+    int rc;
+    if (c->type == B200_KV_F16) rc = launch_part_nt<B200_KV_F16>(a, grid, s);
+    else if (c->type == B200_KV_Q8_0) rc = launch_part_nt<B200_KV_Q8_0>(a, grid, s);
+    else rc = launch_part_nt<B200_KV_Q4_0>(a, grid, s);
+    if (rc != B200_OK) return rc;
+    decode_merge_k<<<dim3(n_slots * q_len, Hq), 64, 0, s>>>(a, gate, out, fo, fm, fl);
+    count_launch(2);
+    return launch_status(who);
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_attn_chunk_keys(void) { return g_chunk_override > 0 ? g_chunk_override : default_chunk(); }
+
+int b200_attn_dec2_nsplit(int Hkv) {
+    (void) Hkv;
+    return 1;   // refined by callers that know n_ctx: chunks = ceil(n_ctx / b200_attn_chunk_keys())
+}
+void b200_attn_dec2_set_nsplit(int n) { (void) n; }
+int b200_attn_dec2_reload_env(void) {
+    const int v = env_chunk();
+    const bool ch = v != default_chunk();
+    g_chunk = v;
+    return ch ? 1 : 0;
+}
+
+int b200_attn_decode2(const float * q, const b200_kv_cache * c, float * out, int T, int p0, const int32_t * p0_dev, int Hq,
+                      float scale, void * stream, const int32_t * pos_rows) {
+    if (T < 1 || T > B200_ATTN_MAX_ROWS) B200_REFUSE(B200_ERR_SHAPE, "attn_decode: unsupported row count %d", T);
+    if (!out) B200_REFUSE(B200_ERR_SHAPE, "attn_decode: out is null");
+    const int max_n = c ? c->n_ctx : 1;
+    // rows of one sequence at consecutive positions share the pass over its KV (up to 4 rows per slot)
+    if (!pos_rows && T <= B200_MAX_QLEN)
+        return decode_impl(q, c, out, nullptr, nullptr, nullptr, nullptr, 1, T, nullptr, p0_dev, p0, max_n, Hq, scale, 0,
+                           (cudaStream_t) stream, "attn_decode");
+    return decode_impl(q, c, out, nullptr, nullptr, nullptr, nullptr, T, 1, pos_rows, p0_dev, p0, max_n, Hq, scale, 0,
+                       (cudaStream_t) stream, "attn_decode");
+}
+
+int b200_attn_decode(const float * q, const b200_kv_cache * c, float * out, int T, int p0, int Hq, float scale, void * stream) {
+    if (c && !c->pt && (p0 < 0 || p0 + T > c->n_ctx)) B200_REFUSE(B200_ERR_SHAPE, "attn_decode: rows %d..%d outside n_ctx %d", p0, p0 + T - 1, c->n_ctx);
+    return b200_attn_decode2(q, c, out, T, p0, nullptr, Hq, scale, stream, nullptr);
+}
+int b200_attn_decode_dev(const float * q, const b200_kv_cache * c, float * out, int T, const int32_t * p0_dev, int max_n, int Hq,
+                         float scale, void * stream) {
+    (void) max_n;
+    if (!p0_dev) B200_REFUSE(B200_ERR_SHAPE, "attn_decode_dev: p0_dev is null");
+    return b200_attn_decode2(q, c, out, T, 0, p0_dev, Hq, scale, stream, nullptr);
+}
+int b200_attn_decode_rows(const float * q, const b200_kv_cache * c, float * out, int T, const int32_t * pos, int Hq, float scale,
+                          void * stream) {
+    if (!pos) B200_REFUSE(B200_ERR_SHAPE, "attn_decode_rows: pos is null");
+    return b200_attn_decode2(q, c, out, T, 0, nullptr, Hq, scale, stream, pos);
+}
+
+int b200_attn_decode_slots(const float * q, const b200_kv_cache * c, float * out, const float * gate, int n_slots, int q_len,
+                           const int32_t * pos, int max_n, int Hq, float scale, int chunk_keys, void * stream) {
+    if (!pos || !out) B200_REFUSE(B200_ERR_SHAPE, "attn_decode_slots: pos / out is null");
+    return decode_impl(q, c, out, gate, nullptr, nullptr, nullptr, n_slots, q_len, pos, nullptr, 0, max_n, Hq, scale, chunk_keys,
+                       (cudaStream_t) stream, "attn_decode_slots");
+}
+
+int b200_attn_decode_slots_partial(const float * q, const b200_kv_cache * c, float * part_o, float * part_m, float * part_l,
+                                   int n_slots, int q_len, const int32_t * pos, int max_n, int Hq, float scale, int chunk_keys,
+                                   void * stream) {
+    if (!pos || !part_o || !part_m || !part_l) B200_REFUSE(B200_ERR_SHAPE, "attn_decode_slots_partial: null argument");
+    if (!aligned16(part_o)) B200_REFUSE(B200_ERR_SHAPE, "attn_decode_slots_partial: part_o must be 16-byte aligned");
+    return decode_impl(q, c, nullptr, nullptr, part_o, part_m, part_l, n_slots, q_len, pos, nullptr, 0, max_n, Hq, scale,
+                       chunk_keys, (cudaStream_t) stream, "attn_decode_slots_partial");
+}
+
+int b200_attn_merge_gate(const float * part_o, const float * part_m, const float * part_l, int nparts, int R, int D,
+                         const float * gate, float * out, void * stream) {
+    if (!part_o || !part_m || !part_l || !out || nparts < 1 || R < 1 || D % 4 || D < 4 || D > 4096 || !aligned16(part_o) ||
+        !aligned16(out) || (gate && !aligned16(gate)))
+        B200_REFUSE(B200_ERR_SHAPE, "attn_merge_gate: unsupported arguments");
+    merge_parts_k<<<R, D / 4, 0, (cudaStream_t) stream>>>(part_o, part_m, part_l, nparts, R, D, gate, out);
+    count_launch();
+    return launch_status("attn_merge_gate");
+}
+
+}  // extern "C"
