@@ -32,6 +32,7 @@ constexpr int PSTR = 144;             // bytes per P row (64 f16 + 16)
 constexpr int SDSTR = 132;            // bytes per V-scale row (64 f16 + 4)
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
+constexpr float PSHIFT = 8.0f;        // P (and l) are kept times 2^8 inside the kernels
 
 template <uint32_t KT> struct traits {
     static constexpr int HB = head_bytes(KT);                       // bytes of a head row in the cache
@@ -282,8 +283,10 @@ __global__ void __launch_bounds__(NTHR) decode_part_k(const dec_args a, const in
                 const float msafe = mnew == B200_NEG_INF ? 0.0f : mnew;
                 fsc[i][e] = ex2f(m_run[i][e] - msafe);
                 m_run[i][e] = mnew;
-                const __half pa = __float2half_rn(S[i][e] == B200_NEG_INF ? 0.0f : ex2f(S[i][e] - msafe));
-                const __half pb = __float2half_rn(S[i][2 + e] == B200_NEG_INF ? 0.0f : ex2f(S[i][2 + e] - msafe));
+                // P carries a factor 2^PSHIFT (numerator and denominator alike): keeps small weights out of the f16
+                // subnormal range
+                const __half pa = __float2half_rn(S[i][e] == B200_NEG_INF ? 0.0f : ex2f(S[i][e] - msafe + PSHIFT));
+                const __half pb = __float2half_rn(S[i][2 + e] == B200_NEG_INF ? 0.0f : ex2f(S[i][2 + e] - msafe + PSHIFT));
                 l_run[i][e] = fmaf(l_run[i][e], fsc[i][e], __half2float(pa) + __half2float(pb));
                 *reinterpret_cast<__half *>(Ps + r * PSTR + kA * 2) = pa;
                 *reinterpret_cast<__half *>(Ps + r * PSTR + kB * 2) = pb;
@@ -363,11 +366,13 @@ __global__ void __launch_bounds__(NTHR) decode_part_k(const dec_args a, const in
                     }
                     const uint32_t sd0 = *reinterpret_cast<const uint32_t *>(Sd + blk * SDSTR + (16 * u + 2 * t) * 2);
                     const uint32_t sd1 = *reinterpret_cast<const uint32_t *>(Sd + blk * SDSTR + (16 * u + 2 * t + 8) * 2);
+                    // block scale of each key pair folded into V (f16 product of an exact integer and the f16 scale)
+                    ax[0] = hmul2_u32(ax[0], sd0); ax[1] = hmul2_u32(ax[1], sd0); ax[2] = hmul2_u32(ax[2], sd1); ax[3] = hmul2_u32(ax[3], sd1);
+                    ay[0] = hmul2_u32(ay[0], sd0); ay[1] = hmul2_u32(ay[1], sd0); ay[2] = hmul2_u32(ay[2], sd1); ay[3] = hmul2_u32(ay[3], sd1);
 #pragma unroll
                     for (int i = 0; i < NT; ++i) {
-                        const uint32_t b0 = hmul2_u32(pw[i][0], sd0), b1 = hmul2_u32(pw[i][1], sd1);
-                        mma16816(O[2 * y][i], ax, b0, b1);
-                        mma16816(O[2 * y + 1][i], ay, b0, b1);
+                        mma16816(O[2 * y][i], ax, pw[i][0], pw[i][1]);
+                        mma16816(O[2 * y + 1][i], ay, pw[i][0], pw[i][1]);
                     }
                 }
             }
@@ -451,9 +456,11 @@ __global__ void __launch_bounds__(64) decode_merge_k(const dec_args a, const flo
         num.x = fmaf(f, o.x, num.x); num.y = fmaf(f, o.y, num.y); num.z = fmaf(f, o.z, num.z); num.w = fmaf(f, o.w, num.w);
     }
     const size_t oi = ((size_t) row * a.Hq + h) * (DH / 4) + threadIdx.x;
-    if (fo) {
-        reinterpret_cast<float4 *>(fo)[oi] = num;
-        if (threadIdx.x == 0) { fm[(size_t) row * a.Hq + h] = M * LN2; fl[(size_t) row * a.Hq + h] = den; }
+    if (fo) {   // public partials are plain sums: take the internal 2^PSHIFT out (exact)
+        constexpr float U = 1.0f / 256.0f;
+        static_assert(PSHIFT == 8.0f, "U must be 2^-PSHIFT");
+        reinterpret_cast<float4 *>(fo)[oi] = make_float4(num.x * U, num.y * U, num.z * U, num.w * U);
+        if (threadIdx.x == 0) { fm[(size_t) row * a.Hq + h] = M * LN2; fl[(size_t) row * a.Hq + h] = den * U; }
     }
     if (out) {
         float4 y = make_float4(0.0f, 0.0f, 0.0f, 0.0f);

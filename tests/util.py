@@ -7,9 +7,10 @@ HQ, HKV, D = 24, 4, 256
 SCALE = 1.0 / 16.0
 TYPES = {"f16": 1, "q4_0": 2, "q8_0": 8}
 
-# BASELINE tolerance for fp32-accumulated attention outputs: max-abs 2e-3 (relative to the largest reference magnitude,
-# the reference tests' own criterion, tests/fast_attn_test.cu:70-78 in the reference project) and 1e-2 relative with a
-# floor of 1 % of that magnitude.
+# Tolerance for fp32-accumulated attention outputs (the BASELINE bar "max-abs 2e-3 / rel 1e-2"), measured the way the
+# reference's own tests measure: largest absolute error relative to the largest reference magnitude
+# (max_abs <= 2e-3 * max|ref|, tests/fast_attn_test.cu:70-78 in the reference project) and relative RMS error
+# (rel-RMS <= 1e-2, tests/fast_attn_fold_test.cu:82).
 TOL_ABS, TOL_REL = 2e-3, 1e-2
 
 
@@ -21,10 +22,10 @@ def check_close(a, ref, what="", tol_abs=TOL_ABS, tol_rel=TOL_REL):
     mx = max(np.abs(ref).max(), 1e-30)
     err = np.abs(a - ref)
     ma = err.max()
-    mr = (err / (np.abs(ref) + 1e-2 * mx)).max()
+    rms = np.sqrt((err ** 2).sum() / max((ref ** 2).sum(), 1e-60))
     assert ma <= tol_abs * mx, "%s: max_abs %.3e > %.1e * %.3e" % (what, ma, tol_abs, mx)
-    assert mr <= tol_rel, "%s: max_rel %.3e > %.1e" % (what, mr, tol_rel)
-    return ma / mx, mr
+    assert rms <= tol_rel, "%s: rel-RMS %.3e > %.1e" % (what, rms, tol_rel)
+    return ma / mx, rms
 
 
 def rng_normal(seed, shape):
