@@ -86,6 +86,13 @@ int b200_attn_prep(const float *qg, const float *k, const float *v, const float 
                    const int32_t *pos, float *q, float *gate, const b200_kv_cache *c, int p0, int T, int Hq, int Hkv,
                    int D, int n_rot, float freq_base, float eps, void *stream, int ldq, int ldk, int ldv,
                    const b200_mrope_pos *mr);
+/* attn_prep with the rotary position and the cache row given separately (new; needed when a sequence's pages are split
+ * over two GPUs: the rotary angle uses the global position rope_pos[t], the row lands at cache_row[t] of this GPU's
+ * compacted sequence, and cache_row[t] < 0 means another GPU owns the row: q and gate are produced, K/V are not stored).
+ * Same arithmetic and bytes as b200_attn_prep. */
+int b200_attn_prep_rows(const float *qg, const float *k, const float *v, const float *q_norm, const float *k_norm,
+                        const int32_t *rope_pos, const int32_t *cache_row, float *q, float *gate, const b200_kv_cache *c,
+                        int T, int Hq, int Hkv, int D, int n_rot, float freq_base, float eps, void *stream);
 /* Prefill form of the append for bf16 activations: k, v [T][Hkv][D] bf16 (raw bits), partial NEOX RoPE applied to K
  * (no norm), quantised into rows p0+t; q [T][Hq][D] bf16 is roped in fp32 and written to q_out [T][Hq][D] f32.
  * No counterpart with bf16 inputs in the reference (its prefill runs k::rope_neox + kv_append on f32,

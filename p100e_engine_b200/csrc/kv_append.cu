@@ -120,7 +120,7 @@ __global__ void prep_k(const TIN * __restrict__ qg, const TIN * __restrict__ k, 
                        const float * __restrict__ qn, const float * __restrict__ kn, const int32_t * __restrict__ pos,
                        float * __restrict__ q, float * __restrict__ gate, kv_view g, int p0, int Hq, int Hkv, int D,
                        int n_rot, float freq_base, float eps, int ldq, int ldk, int ldv, b200_mrope_pos mr,
-                       unsigned * status) {
+                       const int32_t * __restrict__ crow, unsigned * status) {
     extern __shared__ float smr[];   // D floats: the head after norm, rotated in place
     __shared__ float wsum[32];
     const int t = blockIdx.y, b = blockIdx.x, i = threadIdx.x, D4 = D >> 2;
@@ -128,9 +128,10 @@ __global__ void prep_k(const TIN * __restrict__ qg, const TIN * __restrict__ k, 
     const bool isq = b < Hq;
     if (isq && !qg) return;
     const int ppos = pos ? pos[t] : p0 + t;         // rotary position
-    const int row = p0 < 0 ? ppos : p0 + t;         // cache position
+    const int row = crow ? crow[t] : p0 < 0 ? ppos : p0 + t;   // cache position (crow: explicit, < 0 = not stored here)
     unsigned long long roff = 0;
     if (!isq) {
+        if (row < 0) return;
         const int32_t * tab = kv_tab(g, t);
         if (tab && tab[row >> g.psh] < 0) { if (i == 0) atomicOr(status, ST_BAD_PAGE); return; }
         roff = kv_off_tab(g, tab, row);
@@ -293,7 +294,8 @@ int append_impl(const b200_kv_cache * c, const float * k, const float * v, int p
 template <typename TIN, bool NORM, bool SPLITQ>
 int prep_launch(const TIN * qg, const TIN * k, const TIN * v, const float * qn, const float * kn, const int32_t * pos,
                 float * q, float * gate, const b200_kv_cache * c, int p0, int T, int Hq, int Hkv, int D, int n_rot,
-                float freq_base, float eps, cudaStream_t s, int ldq, int ldk, int ldv, const b200_mrope_pos * mr) {
+                float freq_base, float eps, cudaStream_t s, int ldq, int ldk, int ldv, const b200_mrope_pos * mr,
+                const int32_t * crow = nullptr) {
     unsigned * st = device_status_word();
     if (!st) return B200_ERR_CUDA;
     const kv_view g = view_of(*c);
@@ -303,8 +305,8 @@ int prep_launch(const TIN * qg, const TIN * k, const TIN * v, const float * qn, 
     b200_mrope_pos m{};
     const bool use_mr = mr && mr->p;
     if (use_mr) m = *mr;
-#define PREP(KT_) do { if (use_mr) prep_k<KT_, TIN, NORM, SPLITQ, true><<<grid, thr, smem, s>>>(qg, k, v, qn, kn, pos, q, gate, g, p0, Hq, Hkv, D, n_rot, freq_base, eps, ldq, ldk, ldv, m, st); \
-                      else prep_k<KT_, TIN, NORM, SPLITQ, false><<<grid, thr, smem, s>>>(qg, k, v, qn, kn, pos, q, gate, g, p0, Hq, Hkv, D, n_rot, freq_base, eps, ldq, ldk, ldv, m, st); } while (0)
+#define PREP(KT_) do { if (use_mr) prep_k<KT_, TIN, NORM, SPLITQ, true><<<grid, thr, smem, s>>>(qg, k, v, qn, kn, pos, q, gate, g, p0, Hq, Hkv, D, n_rot, freq_base, eps, ldq, ldk, ldv, m, crow, st); \
+                      else prep_k<KT_, TIN, NORM, SPLITQ, false><<<grid, thr, smem, s>>>(qg, k, v, qn, kn, pos, q, gate, g, p0, Hq, Hkv, D, n_rot, freq_base, eps, ldq, ldk, ldv, m, crow, st); } while (0)
     if (c->type == B200_KV_F16) PREP(B200_KV_F16);
     else if (c->type == B200_KV_Q8_0) PREP(B200_KV_Q8_0);
     else PREP(B200_KV_Q4_0);
@@ -376,6 +378,19 @@ int b200_attn_prep(const float * qg, const float * k, const float * v, const flo
     if (mr && mr->p && mr->sect <= 0) B200_REFUSE(B200_ERR_SHAPE, "attn_prep: M-RoPE sections sum to 0");
     return prep_launch<float, true, true>(qg, k, v, q_norm, k_norm, pos, q, gate, c, p0, T, Hq, Hkv, D, n_rot, freq_base,
                                           eps, (cudaStream_t) stream, ldq, ldk, ldv, mr);
+}
+
+int b200_attn_prep_rows(const float * qg, const float * k, const float * v, const float * q_norm, const float * k_norm,
+                        const int32_t * rope_pos, const int32_t * cache_row, float * q, float * gate, const b200_kv_cache * c,
+                        int T, int Hq, int Hkv, int D, int n_rot, float freq_base, float eps, void * stream) {
+    if (T <= 0) return B200_OK;
+    if (!c || !qg || !k || !v || !rope_pos || !cache_row || !q || !gate) B200_REFUSE(B200_ERR_SHAPE, "attn_prep_rows: null argument");
+    if (!type_ok(c->type) || !c->k || c->D != D || c->Hkv != Hkv || D % 128 || D > 1024 || n_rot > D || n_rot % 2 ||
+        !aligned16(qg) || !aligned16(k) || !aligned16(q) || !aligned16(gate) || (q_norm && !aligned16(q_norm)) ||
+        (k_norm && !aligned16(k_norm)))
+        B200_REFUSE(B200_ERR_SHAPE, "attn_prep_rows: unsupported shape / cache / alignment (D=%d Hkv=%d n_rot=%d)", D, Hkv, n_rot);
+    return prep_launch<float, true, true>(qg, k, v, q_norm, k_norm, rope_pos, q, gate, c, -1, T, Hq, Hkv, D, n_rot, freq_base,
+                                          eps, (cudaStream_t) stream, Hq * 2 * D, Hkv * D, Hkv * D, nullptr, cache_row);
 }
 
 int b200_rope_append_bf16(const uint16_t * q, const uint16_t * k, const uint16_t * v, float * q_out,

@@ -1,0 +1,95 @@
+"""Multi-GPU wrapper of the attention path: one process per GPU.
+
+Sharding follows the reference's tensor parallelism — whole KV-head groups per rank (a KV head and its 6 query heads,
+reference src/tp_split.h:45,209-215; per-rank caches sized by the local head count, src/tp_model.cu:3886-3891) — so at
+2 and 4 GPUs attention needs no exchange at all.  With 4 KV heads and 8 GPUs the heads split 4 ways and each sequence's
+pages split 2 ways: the two sequence shards of a head compute unnormalised (O, m, l) over their own keys, all-gather
+them over NCCL (NVLink / NVSwitch) and merge them in shard order with the formula of the reference's split combine
+(dec2_combine_k, src/fast/attn_dec2.cu:430-450), fused with the sigmoid gate.  The received partials land in local
+memory before the merge kernel reads them.
+
+torch.distributed is used for the process group and the all-gather only; all arithmetic runs in libb200attn.so.
+"""
+import numpy as np
+
+from . import pool as P
+
+
+class ShardPlan:
+    """Which KV heads and which sequence shard a rank owns.
+
+    world 1: everything.  world 2 / 4: heads split, n_seq = 1.  world 8 (more ranks than KV heads): head shards =
+    n_kv_heads, the remaining factor splits the sequence; ranks sharing a head group form one merge group.
+    """
+
+    def __init__(self, world, rank, n_kv_heads=4, gqa=6):
+        if world < 1 or rank < 0 or rank >= world:
+            raise ValueError("bad world / rank")
+        self.world, self.rank = world, rank
+        self.n_head_shards = min(world, n_kv_heads)
+        if n_kv_heads % self.n_head_shards or world % self.n_head_shards:
+            raise ValueError("world size %d does not tile %d kv heads" % (world, n_kv_heads))
+        self.n_seq = world // self.n_head_shards
+        self.head_rank = rank // self.n_seq
+        self.seq_rank = rank % self.n_seq
+        self.hkv_local = n_kv_heads // self.n_head_shards
+        self.hq_local = self.hkv_local * gqa
+        self.kv_head0 = self.head_rank * self.hkv_local
+        self.q_head0 = self.kv_head0 * gqa
+
+    def merge_group_ranks(self):
+        """global ranks of the sequence shards that share this rank's heads, in merge order"""
+        return [self.head_rank * self.n_seq + s for s in range(self.n_seq)]
+
+    def all_merge_groups(self):
+        return [[h * self.n_seq + s for s in range(self.n_seq)] for h in range(self.n_head_shards)]
+
+    def local_positions(self, pos, psh=8):
+        return P.local_positions(pos, self.n_seq, self.seq_rank, psh)
+
+    def local_length(self, n, psh=8):
+        return P.local_length(n, self.n_seq, self.seq_rank, psh)
+
+
+class SeqMerge:
+    """All-gather + merge of sequence-shard partials inside one merge group (used only when plan.n_seq > 1)."""
+
+    def __init__(self, plan, rows, hq_local, d=256, device=None, group=None):
+        import torch
+        self.plan, self.rows, self.hq, self.d, self.group = plan, rows, hq_local, d, group
+        R = rows * hq_local
+        self.R = R
+        # one flat send buffer per rank: [O (R*d) | m (R) | l (R)], gathered into [n_seq][R*(d+2)]
+        self.send = torch.zeros(R * (d + 2), dtype=torch.float32, device=device)
+        self.recv = torch.zeros(plan.n_seq, R * (d + 2), dtype=torch.float32, device=device)
+        self.po = torch.zeros(plan.n_seq, R, d, dtype=torch.float32, device=device)
+        self.pm = torch.zeros(plan.n_seq, R, dtype=torch.float32, device=device)
+        self.pl = torch.zeros(plan.n_seq, R, dtype=torch.float32, device=device)
+
+    def views(self):
+        """(part_o, part_m, part_l) views of the send buffer for b200_attn_decode_slots_partial"""
+        R, d = self.R, self.d
+        return self.send[:R * d], self.send[R * d:R * d + R], self.send[R * d + R:]
+
+    def exchange_and_merge(self, gate, out):
+        import torch.distributed as dist
+        from . import fast
+        R, d = self.R, self.d
+        dist.all_gather_into_tensor(self.recv.view(-1), self.send, group=self.group)
+        self.po.copy_(self.recv[:, :R * d].reshape(self.plan.n_seq, R, d))
+        self.pm.copy_(self.recv[:, R * d:R * d + R])
+        self.pl.copy_(self.recv[:, R * d + R:])
+        if not fast.attn_merge_gate(self.po, self.pm, self.pl, self.plan.n_seq, R, d, gate, out):
+            raise RuntimeError("attn_merge_gate refused")
+
+
+def merge_partials_host(parts_o, parts_m, parts_l):
+    """numpy statement of the merge (for CPU tests of the exchange logic): parts_* [n][R][D] / [n][R] -> [R][D]"""
+    parts_o = np.asarray(parts_o, np.float64)
+    parts_m = np.asarray(parts_m, np.float64)
+    parts_l = np.asarray(parts_l, np.float64)
+    M = parts_m.max(axis=0)
+    w = np.where(np.isneginf(parts_m), 0.0, np.exp(parts_m - np.where(np.isneginf(M), 0.0, M)[None, :]))
+    den = (w * parts_l).sum(axis=0)
+    num = (w[:, :, None] * parts_o).sum(axis=0)
+    return np.where(den[:, None] > 0, num / np.where(den > 0, den, 1.0)[:, None], 0.0)

@@ -131,6 +131,13 @@ def attn_prep(qg, k, v, q_norm, k_norm, pos, q, gate, c, p0, T, Hq, Hkv, D, n_ro
                                    ldk, ldv, C.byref(m) if m is not None else None) == L.OK
 
 
+def attn_prep_rows(qg, k, v, q_norm, k_norm, rope_pos, cache_row, q, gate, c, T, Hq, Hkv, D, n_rot, freq_base, eps, s=None):
+    """attn_prep with separate rotary positions and cache rows (cache_row < 0: row owned by another GPU)"""
+    return L.load().b200_attn_prep_rows(L.ptr(qg), L.ptr(k), L.ptr(v), L.ptr(q_norm), L.ptr(k_norm), L.ptr(rope_pos),
+                                        L.ptr(cache_row), L.ptr(q), L.ptr(gate), C.byref(c.c()), T, Hq, Hkv, D, n_rot,
+                                        freq_base, eps, _stream(s)) == L.OK
+
+
 def rope_append_bf16(q, k, v, q_out, c, p0, T, Hq, Hkv, D, n_rot, freq_base, s=None):
     return L.load().b200_rope_append_bf16(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(q_out), C.byref(c.c()), p0, T, Hq, Hkv, D,
                                           n_rot, freq_base, _stream(s)) == L.OK

@@ -45,6 +45,7 @@ SIGNATURES = {
     "b200_kv_append": (I, [KVP, P, P, I, I, P]),
     "b200_kv_append_dev": (I, [KVP, P, P, P, I, P]),
     "b200_attn_prep": (I, [P, P, P, P, P, P, P, P, KVP, I, I, I, I, I, I, F, F, P, I, I, I, C.POINTER(MropePos)]),
+    "b200_attn_prep_rows": (I, [P, P, P, P, P, P, P, P, P, KVP, I, I, I, I, I, F, F, P]),
     "b200_rope_append_bf16": (I, [P, P, P, P, KVP, I, I, I, I, I, I, F, P]),
     "b200_attn_decode": (I, [P, KVP, P, I, I, I, F, P]),
     "b200_attn_decode_dev": (I, [P, KVP, P, I, P, I, I, F, P]),
