@@ -1,10 +1,410 @@
-// Prefill attention entry points (tensor-core kernel under construction in this file).
-#include "common.cuh"
-using namespace b200;
-extern "C" {
-int b200_attn_prefill(const float *, const b200_kv_cache *, float *, int, int, int, float, void *) { B200_REFUSE(B200_ERR_SHAPE, "attn_prefill: not built"); }
-int b200_attn_prefill_variant(const float *, const b200_kv_cache *, float *, int, int, int, float, void *, int) { B200_REFUSE(B200_ERR_SHAPE, "attn_prefill: not built"); }
-size_t b200_attn_fold_scratch_bytes(int, int, int, int) { return 0; }
-int b200_attn_fold(const float *, const b200_kv_cache *, float *, int, int, int, float, void *, size_t, void *, int, int) { B200_REFUSE(B200_ERR_SHAPE, "attn_fold: not built"); }
-int b200_attn_prefill_gated(const float *, const b200_kv_cache *, float *, const float *, int, int, int, float, void *, size_t, void *) { B200_REFUSE(B200_ERR_SHAPE, "attn_prefill: not built"); }
+// Chunked causal prefill attention over the paged f16 / q8_0 / q4_0 cache on the sm_100a tensor cores (tcgen05 + TMEM).
+//
+// Two kernels per call:
+//   kv_tiles_k   dequantises the visible keys once into f16 "tile images" in scratch: per (kv head, 64-key tile) a
+//                32 KB K image and a 32 KB V image laid out exactly as the tensor core reads them from shared memory
+//                (un-swizzled canonical layout, see umma.cuh), so the main kernel fetches a tile with one bulk copy.
+//   prefill_k    one CTA per (128 query rows of one kv head): rows n = 6 t + hh (token t, head hh of the GQA group) on
+//                the MMA M axis.  Per 64-key tile: S = Q K^T (tcgen05.mma, fp32 in tensor memory), online softmax in
+//                base 2 with one thread per row (no shuffles), P to shared memory as f16, O += P V accumulated in
+//                tensor memory.  Warp roles: 4 softmax warps, 1 bulk-copy producer warp, 1 MMA-issue warp; S of
+//                tile j+1 is computed while the softmax of tile j runs.  The running output is rescaled only when a
+//                row's maximum grows by more than 2^8 (P stays below 256 in f16).  Epilogue: O / l, optional sigmoid gate.
+// f16 operands (int8 * f16 scale is not representable in bf16's 8 significand bits), fp32 accumulation.
+//
+// Reference counterparts: attn_fold (src/fast/attn_fold.cu:562-649: per chunk dequantise to f16 in scratch, HFMA2 tile
+// GEMMs on CUDA cores), attn_prefill (src/fast/attn.cu:457-499, fp32 CUDA cores).
+#include "umma.cuh"
+
+#include <algorithm>
+#include <mutex>
+
+namespace b200 {
+namespace {
+
+constexpr int BM = 128;                 // query rows per CTA
+constexpr int BN = 64;                  // keys per tile
+constexpr int IMG = BN * DH * 2;        // bytes of one tile image (32 KB)
+constexpr int Q_BYTES = BM * DH * 2;    // 64 KB
+constexpr int P_BYTES = BM * BN * 2;    // 16 KB
+constexpr int NTHR_PF = 192;            // 4 softmax warps + producer + MMA issuer
+constexpr float LOG2E_PF = 1.4426950408889634f;
+constexpr float RESCALE_GAP = 8.0f;     // rescale O when a row maximum grows by more than this (log2 units)
+
+constexpr int SM_Q = 0;
+constexpr int SM_K = SM_Q + Q_BYTES;            // 2 stages
+constexpr int SM_V = SM_K + 2 * IMG;            // 2 stages
+constexpr int SM_P = SM_V + 2 * IMG;            // 2 buffers
+constexpr int SM_BAR = SM_P + 2 * P_BYTES;      // mbarriers + tmem base
+constexpr int SM_TOTAL = SM_BAR + 256;
+
+// ---- pre-pass: cache rows -> f16 tile images -------------------------------------------------------------------
+// grid (n_tiles, Hkv), 256 threads; thread = (key, 8-dim chunk).  Image byte of (key, dim) = (dim/8)*1024 + key*16 +
+// (dim%8)*2 for K (K-major B operand) and for V (MN-major B operand) alike.  Keys >= n_keys are zero.
+template <uint32_t KT>
+__global__ void __launch_bounds__(256) kv_tiles_k(kv_view g, int n_keys, unsigned char * __restrict__ tiles, int n_tiles,
+                                                  unsigned * status) {
+    const int tile = blockIdx.x, hk = blockIdx.y;
+    unsigned char * kimg = tiles + ((size_t) hk * n_tiles + tile) * (2 * IMG);
+    unsigned char * vimg = kimg + IMG;
+    const int32_t * tab = kv_tab(g, 0);
+    for (int i = threadIdx.x; i < BN * 32; i += 256) {
+        const int key = i & (BN - 1), dc = i >> 6;
+        const int kk = tile * BN + key;
+        uint4 ko = make_uint4(0, 0, 0, 0), vo = ko;
+        if (kk < n_keys) {
+            bool ok = true;
+            if (tab && tab[kk >> g.psh] < 0) { atomicOr(status, ST_BAD_PAGE); ok = false; }
+            if (ok) {
+                const unsigned long long off = kv_off_tab(g, tab, kk) + (unsigned long long) hk * head_bytes(KT);
+                const unsigned char * kr = (const unsigned char *) g.k + off, * vr = (const unsigned char *) g.v + off;
+                if constexpr (KT == B200_KV_F16) {
+                    ko = *reinterpret_cast<const uint4 *>(kr + dc * 16);
+                    vo = *reinterpret_cast<const uint4 *>(vr + dc * 16);
+                } else {
+                    float kf[8], vf[8];
+                    if constexpr (KT == B200_KV_Q8_0) {
+                        const float dk = __half2float(reinterpret_cast<const __half *>(kr)[dc >> 2]);
+                        const float dv = __half2float(reinterpret_cast<const __half *>(vr)[dc >> 2]);
+                        const uint2 qk = *reinterpret_cast<const uint2 *>(kr + 16 + dc * 8);
+                        const uint2 qv = *reinterpret_cast<const uint2 *>(vr + 16 + dc * 8);
+                        const int8_t * a = reinterpret_cast<const int8_t *>(&qk), * b = reinterpret_cast<const int8_t *>(&qv);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) { kf[e] = dk * (float) a[e]; vf[e] = dv * (float) b[e]; }
+                    } else {
+                        const int blk = dc >> 2, sub = dc & 3;   // dims 8 sub .. 8 sub + 7 of the block: bytes (8 sub) % 16 .., nibble sub / 2
+                        const unsigned char * kb = kr + blk * 18, * vb = vr + blk * 18;
+                        const float dk = __half2float(*reinterpret_cast<const __half *>(kb));
+                        const float dv = __half2float(*reinterpret_cast<const __half *>(vb));
+                        const int sh = (sub >> 1) * 4, b0 = 2 + (sub & 1) * 8;
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            kf[e] = dk * (float) ((int) ((kb[b0 + e] >> sh) & 15) - 8);
+                            vf[e] = dv * (float) ((int) ((vb[b0 + e] >> sh) & 15) - 8);
+                        }
+                    }
+                    ko = make_uint4(pack_h2(kf[0], kf[1]), pack_h2(kf[2], kf[3]), pack_h2(kf[4], kf[5]), pack_h2(kf[6], kf[7]));
+                    vo = make_uint4(pack_h2(vf[0], vf[1]), pack_h2(vf[2], vf[3]), pack_h2(vf[4], vf[5]), pack_h2(vf[6], vf[7]));
+                }
+            }
+        }
+        *reinterpret_cast<uint4 *>(kimg + dc * 1024 + key * 16) = ko;
+        *reinterpret_cast<uint4 *>(vimg + dc * 1024 + key * 16) = vo;
+    }
 }
+
+struct pf_args {
+    const float * q;          // [T][Hq][256]
+    const float * gate;       // [T][Hq*256] or nullptr
+    float * out;              // [T][Hq][256]
+    const unsigned char * tiles;
+    int n_tiles;              // tiles per head in scratch
+    int T, p0, Hq, Hkv;
+    float qscale;             // softmax scale * log2(e)
+    unsigned * status;
+};
+
+__device__ __forceinline__ void mbar_arrive(uint64_t * bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    uint64_t * bars = reinterpret_cast<uint64_t *>(smem + SM_BAR);
+    uint64_t * kv_full = bars, * kv_free = bars + 2, * s_full = bars + 4, * s_free = bars + 5, * p_full = bars + 6,
+             * p_free = bars + 8, * o_done = bars + 10;
+    uint32_t * tbase_p = reinterpret_cast<uint32_t *>(bars + 12);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int mtile = (int) gridDim.x - 1 - (int) blockIdx.x;   // heaviest (latest rows) first
+    const int hk = blockIdx.y;
+    const int R = a.T * GQA;                                    // rows of this kv head
+    const int n0 = mtile * BM;
+    const int t_last = min(n0 + BM - 1, R - 1) / GQA;           // last token of the tile
+    const int n_keys_vis = a.p0 + t_last + 1;                   // keys any row of the tile can see
+    const int ntiles = (n_keys_vis + BN - 1) / BN;
+
+    if (tid == 0) {
+        mbar_init(&kv_full[0], 1); mbar_init(&kv_full[1], 1);
+        mbar_init(&kv_free[0], 1); mbar_init(&kv_free[1], 1);
+        mbar_init(s_full, 1); mbar_init(s_free, 128);
+        mbar_init(&p_full[0], 128); mbar_init(&p_full[1], 128);
+        mbar_init(&p_free[0], 1); mbar_init(&p_free[1], 1);
+        mbar_init(o_done, 1);
+        mbar_fence_init();
+    }
+    if (warp == 0) umma::tmem_alloc(tbase_p, 512);
+    // Q rows -> f16, scaled, K-major canonical image: byte(row, d) = (d/8)*2048 + row*16 + (d%8)*2
+    for (int i = tid; i < BM * 32; i += NTHR_PF) {
+        const int r = i & (BM - 1), dc = i >> 7;
+        const int n = n0 + r;
+        uint4 o = make_uint4(0, 0, 0, 0);
+        if (n < R) {
+            const int t = n / GQA, hh = n - t * GQA;
+            const float4 * src = reinterpret_cast<const float4 *>(a.q + ((size_t) t * a.Hq + hk * GQA + hh) * DH + dc * 8);
+            const float4 x = src[0], y = src[1];
+            const float s = a.qscale;
+            o = make_uint4(pack_h2(x.x * s, x.y * s), pack_h2(x.z * s, x.w * s), pack_h2(y.x * s, y.y * s), pack_h2(y.z * s, y.w * s));
+        }
+        *reinterpret_cast<uint4 *>(smem + SM_Q + dc * 2048 + r * 16) = o;
+    }
+    umma::fence_async_smem();
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+    const uint32_t tb = *tbase_p;
+    const uint32_t t_S = tb, t_O = tb + 64;
+
+    if (warp == 4) {
+        // ---------------- producer: one bulk copy per image ----------------
+        if (lane == 0) {
+            const unsigned char * src = a.tiles + (size_t) hk * a.n_tiles * (2 * IMG);
+            for (int j = 0; j < ntiles; ++j) {
+                const int s = j & 1;
+                if (j >= 2) mbar_wait(&kv_free[s], (uint32_t) (((j >> 1) - 1) & 1), a.status);
+                mbar_expect_tx(&kv_full[s], 2 * IMG);
+                bulk_g2s(smem + SM_K + s * IMG, src + (size_t) j * (2 * IMG), IMG, &kv_full[s]);
+                bulk_g2s(smem + SM_V + s * IMG, src + (size_t) j * (2 * IMG) + IMG, IMG, &kv_full[s]);
+            }
+        }
+    } else if (warp == 5) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t id_qk = umma::idesc_f16(BM, BN, false, false);   // S[128 x 64] = Q (K-major) * K^T (K-major)
+            constexpr uint32_t id_pv = umma::idesc_f16(BM, DH, false, true);    // O[128 x 256] += P (K-major) * V (MN-major)
+            const uint32_t q_s = smem_u32(smem + SM_Q);
+            auto issue_qk = [&](int j) {
+                const uint32_t k_s = smem_u32(smem + SM_K + (j & 1) * IMG);
+#pragma unroll 4
+                for (int ks = 0; ks < DH / 16; ++ks)
+                    umma::mma_ss(t_S, umma::smem_desc(q_s + ks * 2 * 2048, 2048, 128), umma::smem_desc(k_s + ks * 2 * 1024, 1024, 128),
+                                 id_qk, ks > 0);
+                umma::commit(s_full);
+            };
+            mbar_wait(&kv_full[0], 0, a.status);
+            umma::fence_after_sync();
+            issue_qk(0);
+            for (int j = 0; j < ntiles; ++j) {
+                if (j + 1 < ntiles) {
+                    mbar_wait(&kv_full[(j + 1) & 1], (uint32_t) (((j + 1) >> 1) & 1), a.status);
+                    mbar_wait(s_free, (uint32_t) (j & 1), a.status);      // softmax has S_j in registers
+                    umma::fence_after_sync();
+                    issue_qk(j + 1);
+                }
+                mbar_wait(&p_full[j & 1], (uint32_t) ((j >> 1) & 1), a.status);
+                umma::fence_after_sync();
+                const uint32_t p_s = smem_u32(smem + SM_P + (j & 1) * P_BYTES), v_s = smem_u32(smem + SM_V + (j & 1) * IMG);
+#pragma unroll
+                for (int ks = 0; ks < BN / 16; ++ks)   // V image: MN-major, key groups of 8 contiguous (LBO 128), dim groups 1024 apart
+                    umma::mma_ss(t_O, umma::smem_desc(p_s + ks * 2 * 2048, 2048, 128), umma::smem_desc(v_s + ks * 2 * 128, 128, 1024),
+                                 id_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                umma::commit(&kv_free[j & 1]);
+                umma::commit(&p_free[j & 1]);
+            }
+            umma::commit(o_done);
+        }
+    } else {
+        // ---------------- softmax: thread = row ----------------
+        const int r = tid, n = n0 + r;
+        const int t_row = n / GQA;
+        const int pos = n < R ? a.p0 + t_row : -1;
+        const uint32_t lane_off = (uint32_t) (warp * 32) << 16;
+        float m_ref = B200_NEG_INF, l = 0.0f;
+        for (int j = 0; j < ntiles; ++j) {
+            mbar_wait(s_full, (uint32_t) (j & 1), a.status);
+            umma::fence_after_sync();
+            uint32_t sr[2][32];
+            umma::tmem_ld32(t_S + lane_off, sr[0]);
+            umma::tmem_ld32(t_S + lane_off + 32, sr[1]);
+            umma::tmem_ld_wait();
+            umma::fence_before_sync();
+            mbar_arrive(s_free);
+            const int k0 = j * BN;
+            float mx = B200_NEG_INF;
+            const bool diag = k0 + BN - 1 > pos;   // some key of the tile is masked for this row
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    float s = __uint_as_float(sr[h][c]);
+                    if (diag && k0 + 32 * h + c > pos) s = B200_NEG_INF;
+                    sr[h][c] = __float_as_uint(s);
+                    mx = fmaxf(mx, s);
+                }
+            // lazy rescale: only when some row of the warp outgrew its reference maximum
+            const bool grow = mx > m_ref + RESCALE_GAP || (m_ref == B200_NEG_INF && mx != B200_NEG_INF);
+            if (__any_sync(0xffffffffu, grow)) {
+                float f = 1.0f;
+                if (grow) {
+                    f = m_ref == B200_NEG_INF ? 0.0f : ex2f(m_ref - mx);
+                    m_ref = mx;
+                    l *= f;
+                }
+                if (j > 0) {
+                    mbar_wait(&p_free[(j - 1) & 1], (uint32_t) (((j - 1) >> 1) & 1), a.status);   // P V of tile j-1 has landed in O
+                    umma::fence_after_sync();
+#pragma unroll 1
+                    for (int c0 = 0; c0 < DH; c0 += 32) {
+                        uint32_t o[32];
+                        umma::tmem_ld32(t_O + lane_off + c0, o);
+                        umma::tmem_ld_wait();
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * f);
+                        umma::tmem_st32(t_O + lane_off + c0, o);
+                    }
+                    umma::tmem_st_wait();
+                }
+            }
+            const float mref_safe = m_ref == B200_NEG_INF ? 0.0f : m_ref;
+            if (j >= 2) mbar_wait(&p_free[j & 1], (uint32_t) (((j >> 1) - 1) & 1), a.status);   // P buffer no longer read
+            unsigned char * prow = smem + SM_P + (j & 1) * P_BYTES + r * 16;
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int c8 = 0; c8 < 4; ++c8) {
+                    uint32_t w4[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float s0 = __uint_as_float(sr[h][c8 * 8 + 2 * e]), s1 = __uint_as_float(sr[h][c8 * 8 + 2 * e + 1]);
+                        const __half2 p2 = __floats2half2_rn(s0 == B200_NEG_INF ? 0.0f : ex2f(s0 - mref_safe),
+                                                             s1 == B200_NEG_INF ? 0.0f : ex2f(s1 - mref_safe));
+                        const float2 pf = __half22float2(p2);
+                        l += pf.x + pf.y;
+                        w4[e] = *reinterpret_cast<const uint32_t *>(&p2);
+                    }
+                    // key chunk kc = 4 h + c8 of the K-major P image: byte = kc * 2048 + row * 16
+                    *reinterpret_cast<uint4 *>(prow + (4 * h + c8) * 2048) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+                }
+            umma::fence_async_smem();
+            umma::fence_before_sync();
+            mbar_arrive(&p_full[j & 1]);
+        }
+        // ---------------- epilogue: O / l, gate, store ----------------
+        mbar_wait(o_done, 0, a.status);
+        umma::fence_after_sync();
+        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+        const int hh = n - t_row * GQA;
+        const size_t orow = ((size_t) t_row * a.Hq + hk * GQA + hh) * DH;
+#pragma unroll 1
+        for (int c0 = 0; c0 < DH; c0 += 32) {
+            uint32_t o[32];
+            umma::tmem_ld32(t_O + lane_off + c0, o);
+            umma::tmem_ld_wait();
+            if (n < R) {
+#pragma unroll
+                for (int c = 0; c < 32; c += 4) {
+                    float4 y = make_float4(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv,
+                                           __uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
+                    if (a.gate) {
+                        const float4 gv = *reinterpret_cast<const float4 *>(a.gate + orow + c0 + c);
+                        y.x *= 1.0f / (1.0f + expf(-gv.x)); y.y *= 1.0f / (1.0f + expf(-gv.y));
+                        y.z *= 1.0f / (1.0f + expf(-gv.z)); y.w *= 1.0f / (1.0f + expf(-gv.w));
+                    }
+                    *reinterpret_cast<float4 *>(a.out + orow + c0 + c) = y;
+                }
+            }
+        }
+    }
+    umma::fence_before_sync();
+    __syncthreads();
+    if (warp == 0) umma::tmem_dealloc(tb, 512);
+}
+
+// ------------------------------------------------------------------------------------------------ host side ----
+size_t scratch_need(int n_keys, int Hkv) {
+    const size_t n_tiles = (size_t) (n_keys + BN - 1) / BN;
+    return n_tiles * Hkv * (2 * IMG) + 256;
+}
+
+struct own_scratch { int dev = -1; void * p = nullptr; size_t cap = 0; };
+own_scratch g_own[16];
+std::mutex g_pf_mu;
+
+void * own_scratch_for(size_t bytes, cudaStream_t s) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lk(g_pf_mu);
+    own_scratch & e = g_own[dev & 15];
+    if (bytes > e.cap) {
+        if (e.p) { cudaStreamSynchronize(s); cudaFree(e.p); e.p = nullptr; e.cap = 0; }
+        if (cudaMalloc(&e.p, bytes) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+        e.cap = bytes;
+    }
+    return e.p;
+}
+
+int prefill_impl(const float * q, const b200_kv_cache * c, float * out, const float * gate, int T, int p0, int Hq, float scale,
+                 void * scratch, size_t scratch_bytes, cudaStream_t s, const char * who) {
+    if (!c || !q || !out || !c->k || !c->v) B200_REFUSE(B200_ERR_SHAPE, "%s: null argument", who);
+    if (c->D != DH || Hq != GQA * c->Hkv || c->Hkv <= 0 || T < 1 || p0 < 0)
+        B200_REFUSE(B200_ERR_SHAPE, "%s: unsupported shape (D=%d Hq=%d Hkv=%d T=%d p0=%d)", who, c->D, Hq, c->Hkv, T, p0);
+    if (c->type != B200_KV_F16 && c->type != B200_KV_Q8_0 && c->type != B200_KV_Q4_0) B200_REFUSE(B200_ERR_SHAPE, "%s: unsupported cache type %u", who, c->type);
+    if (!aligned16(c->k) || !aligned16(c->v) || !aligned16(q) || !aligned16(out) || (gate && !aligned16(gate)) || (c->pt && c->pstride % 16))
+        B200_REFUSE(B200_ERR_SHAPE, "%s: cache base, page stride, q, out and gate must be 16-byte aligned", who);
+    if (!c->pt && p0 + T > c->n_ctx) B200_REFUSE(B200_ERR_SHAPE, "%s: rows %d..%d outside n_ctx %d", who, p0, p0 + T - 1, c->n_ctx);
+    const int n_keys = p0 + T;
+    const size_t need = scratch_need(n_keys, c->Hkv);
+    if (!scratch) {
+        scratch = own_scratch_for(need, s);
+        if (!scratch) B200_REFUSE(B200_ERR_ALLOC, "%s: %zu bytes of scratch could not be allocated", who, need);
+    } else if (scratch_bytes < need || ((uintptr_t) scratch & 255)) {
+        B200_REFUSE(B200_ERR_SCRATCH, "%s: scratch too small or not 256-byte aligned (%zu bytes given, %zu needed for %d keys)", who,
+                    scratch_bytes, need, n_keys);
+    }
+    unsigned * st = device_status_word();
+    if (!st) return B200_ERR_CUDA;
+    static bool attr_done[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_done[dev & 63]) {
+        if (cudaFuncSetAttribute(prefill_k, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_TOTAL) != cudaSuccess)
+            return launch_status("attn_prefill (shared memory attribute)");
+        attr_done[dev & 63] = true;
+    }
+    const int n_tiles = (n_keys + BN - 1) / BN;
+    const kv_view g = view_of(*c);
+    const dim3 tg(n_tiles, c->Hkv);
+    if (c->type == B200_KV_F16) kv_tiles_k<B200_KV_F16><<<tg, 256, 0, s>>>(g, n_keys, (unsigned char *) scratch, n_tiles, st);
+    else if (c->type == B200_KV_Q8_0) kv_tiles_k<B200_KV_Q8_0><<<tg, 256, 0, s>>>(g, n_keys, (unsigned char *) scratch, n_tiles, st);
+    else kv_tiles_k<B200_KV_Q4_0><<<tg, 256, 0, s>>>(g, n_keys, (unsigned char *) scratch, n_tiles, st);
+    pf_args a;
+    a.q = q; a.gate = gate; a.out = out; a.tiles = (const unsigned char *) scratch; a.n_tiles = n_tiles;
+    a.T = T; a.p0 = p0; a.Hq = Hq; a.Hkv = c->Hkv; a.qscale = scale * LOG2E_PF; a.status = st;
+    const int n_mtiles = (T * GQA + BM - 1) / BM;
+    prefill_k<<<dim3(n_mtiles, c->Hkv), NTHR_PF, SM_TOTAL, s>>>(a);
+    count_launch(2);
+    return launch_status(who);
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_attn_prefill(const float * q, const b200_kv_cache * c, float * out, int T, int p0, int Hq, float scale, void * stream) {
+    return prefill_impl(q, c, out, nullptr, T, p0, Hq, scale, nullptr, 0, (cudaStream_t) stream, "attn_prefill");
+}
+int b200_attn_prefill_variant(const float * q, const b200_kv_cache * c, float * out, int T, int p0, int Hq, float scale, void * stream,
+                              int variant) {
+    (void) variant;   // the reference's variants are bitwise-equal schedules of one fp32 algorithm; there is one kernel here
+    return prefill_impl(q, c, out, nullptr, T, p0, Hq, scale, nullptr, 0, (cudaStream_t) stream, "attn_prefill");
+}
+// scratch for a call whose visible context (p0 + T) is at most `chunk` keys; chunk <= 0: T keys (p0 = 0). nsplit unused.
+size_t b200_attn_fold_scratch_bytes(int T, int Hkv, int chunk, int nsplit) {
+    (void) nsplit;
+    return scratch_need(chunk > 0 ? chunk : T, Hkv);
+}
+int b200_attn_fold(const float * q, const b200_kv_cache * c, float * out, int T, int p0, int Hq, float scale, void * scratch,
+                   size_t scratch_bytes, void * stream, int chunk, int nsplit) {
+    (void) chunk; (void) nsplit;
+    if (!scratch) B200_REFUSE(B200_ERR_SCRATCH, "attn_fold: scratch is null");
+    return prefill_impl(q, c, out, nullptr, T, p0, Hq, scale, scratch, scratch_bytes, (cudaStream_t) stream, "attn_fold");
+}
+int b200_attn_prefill_gated(const float * q, const b200_kv_cache * c, float * out, const float * gate, int T, int p0, int Hq,
+                            float scale, void * scratch, size_t scratch_bytes, void * stream) {
+    return prefill_impl(q, c, out, gate, T, p0, Hq, scale, scratch, scratch_bytes, (cudaStream_t) stream, "attn_prefill_gated");
+}
+
+}  // extern "C"
