@@ -9,6 +9,9 @@ Workloads (synthetic, seeded; shapes of the configurations the baseline names):
   verify8     8 slots x q_len 4, contexts ~U{1024..32768}, one layer
   long_q4     16 slots x q_len 1, context 131072 each, q4_0, one layer
   decode1     1 slot x q_len 1, context 4096, one layer (latency-bound)
+  prefill8k   one sequence, 8192 new tokens, no prior context: bf16 Q/K/V -> partial RoPE + quantise + append (q8_0
+              pages), tensor-core causal attention over the quantised cache, sigmoid gate; metric = attention
+              TFLOP/s with FLOPs = 4 * D * Hq * T^2 / 2 (the reference's count, tests/fast_attn_fold_test.cu:83)
 A step = for every layer: attn_prep of the step's rows (norm + partial RoPE + quantise + append into the pages) and
 the split-KV attention of all slots with the fused sigmoid gate.  metric = KV bytes read per second, counted once per
 slot and layer: sum_slots n_ctx * Hkv * 2 * head_bytes (the reference's own definition, tests/fast_attn_test.cu:277
@@ -41,6 +44,8 @@ WORKLOADS = {
     "verify8": (8, 4, 1024, 32768, 1, "q8_0"),
     "long_q4": (16, 1, 131072, 131072, 1, "q4_0"),
     "decode1": (1, 1, 4096, 4096, 1, "q8_0"),
+    # chunked causal prefill: one sequence, T new tokens, p0 = 0 (slots, q_len unused; ctx = T)
+    "prefill8k": (1, 0, 8192, 8192, 1, "q8_0"),
 }
 
 
@@ -409,10 +414,135 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
+def run_prefill(args):
+    """prefill8k on one GPU (N > 1: every rank runs its KV-head shard of the same sequence)"""
+    import torch
+    import torch.distributed as dist
+    from p100e_engine_b200 import dist as Dm, fast, lib as L
+    from p100e_engine_b200 import pool as P
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device (this path has no CPU fallback)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    lib = L.load()
+    nshard = min(world, HKV)
+    if world > HKV:
+        raise SystemExit("bench.py: prefill8k shards KV heads only (N <= 4)")
+    hkv, hq = HKV // nshard, HQ // nshard
+    T = WORKLOADS[args.workload][2]
+    kt = KV_TYPES[args.kv or WORKLOADS[args.workload][5]]
+    n_pages = T >> PSH
+    layout = P.PoolLayout(kt, hkv, 1, n_pages, PSH, D)
+    pool = torch.zeros(layout.total_bytes, dtype=torch.uint8, device=dev)
+    pt = torch.from_numpy(np.random.default_rng(args.seed).permutation(n_pages).astype(np.int32)).to(dev)
+    c = fast.kv_cache(kt, T, hkv, D, pool.data_ptr() + layout.k_offset(0), pool.data_ptr() + layout.v_offset(0), pt, None, PSH,
+                      layout.pstride)
+    g = torch.Generator(device="cpu").manual_seed(args.seed + rank)
+    h_q = torch.randn(T, hq, D, generator=g).to(torch.bfloat16).pin_memory()
+    h_k = torch.randn(T, hkv, D, generator=g).to(torch.bfloat16).pin_memory()
+    h_v = torch.randn(T, hkv, D, generator=g).to(torch.bfloat16).pin_memory()
+    h_g = torch.randn(T, hq * D, generator=g).pin_memory()
+    h_o = torch.empty(T, hq, D).pin_memory()
+    d_q, d_k, d_v, d_g = h_q.to(dev), h_k.to(dev), h_v.to(dev), h_g.to(dev)
+    s_q, s_k, s_v, s_g = [torch.empty_like(x) for x in (d_q, d_k, d_v, d_g)]
+    qr = torch.empty(T, hq, D, device=dev)
+    out = torch.empty(T, hq, D, device=dev)
+    nb = fast.attn_fold_scratch_bytes(T, hkv, T)
+    scratch = torch.empty(nb, dtype=torch.uint8, device=dev)
+
+    def step(q, k, v, gt, ev=None):
+        ok = fast.rope_append_bf16(q, k, v, qr, c, 0, T, hq, hkv, D, N_ROT, ROPE_BASE)
+        if ev is not None:
+            ev[0].record()
+        ok = ok and fast.attn_prefill_gated(qr, c, out, gt, T, 0, hq, SCALE, scratch, nb)
+        if ev is not None:
+            ev[1].record()
+        if not ok:
+            raise RuntimeError("a library call was refused")
+
+    def step_e2e():
+        s_q.copy_(h_q, non_blocking=True); s_k.copy_(h_k, non_blocking=True)
+        s_v.copy_(h_v, non_blocking=True); s_g.copy_(h_g, non_blocking=True)
+        step(s_q, s_k, s_v, s_g)
+        h_o.copy_(out, non_blocking=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(steps):
+            fn(i)
+        b.record()
+        barrier()
+        ms = torch.tensor([a.elapsed_time(b)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(max(args.warmup, 3)):
+        step(d_q, d_k, d_v, d_g)
+    events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    clk = ClockSampler(local)
+    clk.start()
+    n0 = lib.b200_launch_count()
+    ms_total = timed(lambda i: step(d_q, d_k, d_v, d_g, events[i]), args.steps)
+    launches = lib.b200_launch_count() - n0
+    clocks = clk.stop()
+    att_ms = float(np.mean([e0.elapsed_time(e1) for e0, e1 in events]))
+    for _ in range(3):
+        step_e2e()
+    ms_e2e = timed(lambda i: step_e2e(), args.steps)
+    if lib.b200_last_device_status(None):
+        raise SystemExit("bench.py: a kernel recorded a device status")
+    if rank == 0:
+        flops = 4.0 * D * HQ * (T * T / 2.0)
+        ms_step = ms_total / args.steps
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except OSError:
+            pass
+        peak = float(peaks.get("bf16_tflops", 1590.0))
+        ach = flops / nshard / (att_ms * 1e-3) / 1e12
+        line = {"metric": "prefill_attn_tflops", "value": flops / (ms_step * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "f16 operands, fp32 accumulate", "data": "synthetic",
+                "config": {"workload": args.workload, "kv": args.kv or "q8_0", "T": T, "p0": 0, "heads": "24q/4kv", "head_dim": D,
+                           "page": 1 << PSH, "parallelism": "kv-head shards %d" % nshard,
+                           "l2": "K/V tile images (%.1f MB) and Q/out (%.0f MB) exceed no cache assumption: inputs larger than L2" % (nb / 1e6, 2 * T * hq * D * 4 / 1e6),
+                           "step": "rope_append_bf16 (RoPE + quantise + append) + attn_prefill_gated (dequantise to f16 tiles + tcgen05 attention + gate)"},
+                "clocks": clocks, "gpu_launches": int(launches),
+                "e2e": {"value": flops / (ms_e2e / args.steps * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e / args.steps,
+                        "h2d_bytes_per_step": int(sum(x.numel() * x.element_size() for x in (h_q, h_k, h_v, h_g))),
+                        "d2h_bytes_per_step": int(h_o.numel() * 4)},
+                "roofline": {"bound": "tensor", "kernel": "kv_tiles_k + prefill_k", "achieved": ach, "peak": peak,
+                             "peak_source": "measured burst" if peaks else "fallback", "unit": "TFLOP/s", "frac": ach / peak,
+                             "traffic": None, "avg_launch_ms": att_ms, "algorithmic_flops_per_launch": flops / nshard}}
+        if not args.no_cpu_baseline:
+            line["cpu_baseline"] = {"value": None, "unit": "TFLOP/s", "cores": 0, "kind": "reference",
+                                    "sample": "not timed for prefill: see the decode workloads for the CPU attention baseline"}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     args = parse()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "prefill8k":
+        run_prefill(args)
     else:
         run_b200(args)
 

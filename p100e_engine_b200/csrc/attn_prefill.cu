@@ -8,7 +8,7 @@
 //                the MMA M axis.  Per 64-key tile: S = Q K^T (tcgen05.mma, fp32 in tensor memory), online softmax in
 //                base 2 with one thread per row (no shuffles), P to shared memory as f16, O += P V accumulated in
 //                tensor memory.  Warp roles: 4 softmax warps, 1 bulk-copy producer warp, 1 MMA-issue warp; S of
-//                tile j+1 is computed while the softmax of tile j runs.  The running output is rescaled only when a
+//                tile j+1 is computed (second S buffer in tensor memory) while the softmax of tile j runs.  The running output is rescaled only when a
 //                row's maximum grows by more than 2^8 (P stays below 256 in f16).  Epilogue: O / l, optional sigmoid gate.
 // f16 operands (int8 * f16 scale is not representable in bf16's 8 significand bits), fp32 accumulation.
 //
@@ -111,9 +111,9 @@ __device__ __forceinline__ void mbar_arrive(uint64_t * bar) {
 __global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
     extern __shared__ __align__(1024) unsigned char smem[];
     uint64_t * bars = reinterpret_cast<uint64_t *>(smem + SM_BAR);
-    uint64_t * kv_full = bars, * kv_free = bars + 2, * s_full = bars + 4, * s_free = bars + 5, * p_full = bars + 6,
-             * p_free = bars + 8, * o_done = bars + 10;
-    uint32_t * tbase_p = reinterpret_cast<uint32_t *>(bars + 12);
+    uint64_t * k_full = bars, * k_free = bars + 2, * v_full = bars + 4, * v_free = bars + 6, * s_full = bars + 8,
+             * s_free = bars + 10, * p_full = bars + 12, * p_free = bars + 14, * o_done = bars + 16;
+    uint32_t * tbase_p = reinterpret_cast<uint32_t *>(bars + 18);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int mtile = (int) gridDim.x - 1 - (int) blockIdx.x;   // heaviest (latest rows) first
@@ -125,11 +125,12 @@ __global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
     const int ntiles = (n_keys_vis + BN - 1) / BN;
 
     if (tid == 0) {
-        mbar_init(&kv_full[0], 1); mbar_init(&kv_full[1], 1);
-        mbar_init(&kv_free[0], 1); mbar_init(&kv_free[1], 1);
-        mbar_init(s_full, 1); mbar_init(s_free, 128);
-        mbar_init(&p_full[0], 128); mbar_init(&p_full[1], 128);
-        mbar_init(&p_free[0], 1); mbar_init(&p_free[1], 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&k_full[b], 1); mbar_init(&k_free[b], 1);
+            mbar_init(&v_full[b], 1); mbar_init(&v_free[b], 1);
+            mbar_init(&s_full[b], 1); mbar_init(&s_free[b], 128);
+            mbar_init(&p_full[b], 128); mbar_init(&p_free[b], 1);
+        }
         mbar_init(o_done, 1);
         mbar_fence_init();
     }
@@ -153,53 +154,56 @@ __global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
     __syncthreads();
     umma::fence_after_sync();
     const uint32_t tb = *tbase_p;
-    const uint32_t t_S = tb, t_O = tb + 64;
+    const uint32_t t_S = tb, t_O = tb + 2 * BN;   // S double-buffered at columns 0 and 64, O behind them
 
     if (warp == 4) {
-        // ---------------- producer: one bulk copy per image ----------------
+        // ---------------- producer: one bulk copy per image; K and V rings are released separately ----------------
         if (lane == 0) {
             const unsigned char * src = a.tiles + (size_t) hk * a.n_tiles * (2 * IMG);
             for (int j = 0; j < ntiles; ++j) {
                 const int s = j & 1;
-                if (j >= 2) mbar_wait(&kv_free[s], (uint32_t) (((j >> 1) - 1) & 1), a.status);
-                mbar_expect_tx(&kv_full[s], 2 * IMG);
-                bulk_g2s(smem + SM_K + s * IMG, src + (size_t) j * (2 * IMG), IMG, &kv_full[s]);
-                bulk_g2s(smem + SM_V + s * IMG, src + (size_t) j * (2 * IMG) + IMG, IMG, &kv_full[s]);
+                const uint32_t ph = (uint32_t) (((j >> 1) - 1) & 1);
+                if (j >= 2) mbar_wait(&k_free[s], ph, a.status);        // Q K^T of tile j-2 has read the stage
+                mbar_expect_tx(&k_full[s], IMG);
+                bulk_g2s(smem + SM_K + s * IMG, src + (size_t) j * (2 * IMG), IMG, &k_full[s]);
+                if (j >= 2) mbar_wait(&v_free[s], ph, a.status);        // P V of tile j-2 has read the stage
+                mbar_expect_tx(&v_full[s], IMG);
+                bulk_g2s(smem + SM_V + s * IMG, src + (size_t) j * (2 * IMG) + IMG, IMG, &v_full[s]);
             }
         }
     } else if (warp == 5) {
-        // ---------------- MMA issuer ----------------
+        // ---------------- MMA issuer: Q K^T of tile j+1 is queued before P V of tile j ----------------
         if (lane == 0) {
             constexpr uint32_t id_qk = umma::idesc_f16(BM, BN, false, false);   // S[128 x 64] = Q (K-major) * K^T (K-major)
             constexpr uint32_t id_pv = umma::idesc_f16(BM, DH, false, true);    // O[128 x 256] += P (K-major) * V (MN-major)
             const uint32_t q_s = smem_u32(smem + SM_Q);
             auto issue_qk = [&](int j) {
-                const uint32_t k_s = smem_u32(smem + SM_K + (j & 1) * IMG);
+                const int b = j & 1;
+                mbar_wait(&k_full[b], (uint32_t) ((j >> 1) & 1), a.status);
+                if (j >= 2) mbar_wait(&s_free[b], (uint32_t) (((j >> 1) - 1) & 1), a.status);   // softmax of tile j-2 holds S in registers
+                umma::fence_after_sync();
+                const uint32_t k_s = smem_u32(smem + SM_K + b * IMG);
 #pragma unroll 4
                 for (int ks = 0; ks < DH / 16; ++ks)
-                    umma::mma_ss(t_S, umma::smem_desc(q_s + ks * 2 * 2048, 2048, 128), umma::smem_desc(k_s + ks * 2 * 1024, 1024, 128),
-                                 id_qk, ks > 0);
-                umma::commit(s_full);
+                    umma::mma_ss(t_S + b * BN, umma::smem_desc(q_s + ks * 2 * 2048, 2048, 128),
+                                 umma::smem_desc(k_s + ks * 2 * 1024, 1024, 128), id_qk, ks > 0);
+                umma::commit(&s_full[b]);
+                umma::commit(&k_free[b]);
             };
-            mbar_wait(&kv_full[0], 0, a.status);
-            umma::fence_after_sync();
             issue_qk(0);
             for (int j = 0; j < ntiles; ++j) {
-                if (j + 1 < ntiles) {
-                    mbar_wait(&kv_full[(j + 1) & 1], (uint32_t) (((j + 1) >> 1) & 1), a.status);
-                    mbar_wait(s_free, (uint32_t) (j & 1), a.status);      // softmax has S_j in registers
-                    umma::fence_after_sync();
-                    issue_qk(j + 1);
-                }
-                mbar_wait(&p_full[j & 1], (uint32_t) ((j >> 1) & 1), a.status);
+                if (j + 1 < ntiles) issue_qk(j + 1);
+                const int b = j & 1;
+                mbar_wait(&v_full[b], (uint32_t) ((j >> 1) & 1), a.status);
+                mbar_wait(&p_full[b], (uint32_t) ((j >> 1) & 1), a.status);
                 umma::fence_after_sync();
-                const uint32_t p_s = smem_u32(smem + SM_P + (j & 1) * P_BYTES), v_s = smem_u32(smem + SM_V + (j & 1) * IMG);
+                const uint32_t p_s = smem_u32(smem + SM_P + b * P_BYTES), v_s = smem_u32(smem + SM_V + b * IMG);
 #pragma unroll
                 for (int ks = 0; ks < BN / 16; ++ks)   // V image: MN-major, key groups of 8 contiguous (LBO 128), dim groups 1024 apart
                     umma::mma_ss(t_O, umma::smem_desc(p_s + ks * 2 * 2048, 2048, 128), umma::smem_desc(v_s + ks * 2 * 128, 128, 1024),
                                  id_pv, (j > 0 || ks > 0) ? 1u : 0u);
-                umma::commit(&kv_free[j & 1]);
-                umma::commit(&p_free[j & 1]);
+                umma::commit(&v_free[b]);
+                umma::commit(&p_free[b]);
             }
             umma::commit(o_done);
         }
@@ -211,14 +215,14 @@ __global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
         const uint32_t lane_off = (uint32_t) (warp * 32) << 16;
         float m_ref = B200_NEG_INF, l = 0.0f;
         for (int j = 0; j < ntiles; ++j) {
-            mbar_wait(s_full, (uint32_t) (j & 1), a.status);
+            mbar_wait(&s_full[j & 1], (uint32_t) ((j >> 1) & 1), a.status);
             umma::fence_after_sync();
             uint32_t sr[2][32];
-            umma::tmem_ld32(t_S + lane_off, sr[0]);
-            umma::tmem_ld32(t_S + lane_off + 32, sr[1]);
+            umma::tmem_ld32(t_S + (j & 1) * BN + lane_off, sr[0]);
+            umma::tmem_ld32(t_S + (j & 1) * BN + lane_off + 32, sr[1]);
             umma::tmem_ld_wait();
             umma::fence_before_sync();
-            mbar_arrive(s_free);
+            mbar_arrive(&s_free[j & 1]);
             const int k0 = j * BN;
             float mx = B200_NEG_INF;
             const bool diag = k0 + BN - 1 > pos;   // some key of the tile is masked for this row
