@@ -157,16 +157,19 @@ __global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
     const uint32_t t_S = tb, t_O = tb + 2 * BN;   // S double-buffered at columns 0 and 64, O behind them
 
     if (warp == 4) {
-        // ---------------- producer: one bulk copy per image; K and V rings are released separately ----------------
+        // ---------------- producer: one bulk copy per image; K (lane 0) and V (lane 16) rings run independently ----------------
+        const unsigned char * src = a.tiles + (size_t) hk * a.n_tiles * (2 * IMG);
         if (lane == 0) {
-            const unsigned char * src = a.tiles + (size_t) hk * a.n_tiles * (2 * IMG);
             for (int j = 0; j < ntiles; ++j) {
                 const int s = j & 1;
-                const uint32_t ph = (uint32_t) (((j >> 1) - 1) & 1);
-                if (j >= 2) mbar_wait(&k_free[s], ph, a.status);        // Q K^T of tile j-2 has read the stage
+                if (j >= 2) mbar_wait(&k_free[s], (uint32_t) (((j >> 1) - 1) & 1), a.status);   // Q K^T of tile j-2 has read the stage
                 mbar_expect_tx(&k_full[s], IMG);
                 bulk_g2s(smem + SM_K + s * IMG, src + (size_t) j * (2 * IMG), IMG, &k_full[s]);
-                if (j >= 2) mbar_wait(&v_free[s], ph, a.status);        // P V of tile j-2 has read the stage
+            }
+        } else if (lane == 16) {
+            for (int j = 0; j < ntiles; ++j) {
+                const int s = j & 1;
+                if (j >= 2) mbar_wait(&v_free[s], (uint32_t) (((j >> 1) - 1) & 1), a.status);   // P V of tile j-2 has read the stage
                 mbar_expect_tx(&v_full[s], IMG);
                 bulk_g2s(smem + SM_V + s * IMG, src + (size_t) j * (2 * IMG) + IMG, IMG, &v_full[s]);
             }
@@ -224,17 +227,20 @@ __global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
             umma::fence_before_sync();
             mbar_arrive(&s_free[j & 1]);
             const int k0 = j * BN;
-            float mx = B200_NEG_INF;
             const bool diag = k0 + BN - 1 > pos;   // some key of the tile is masked for this row
+            if (__any_sync(0xffffffffu, diag)) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int c = 0; c < 32; ++c)
+                        if (k0 + 32 * h + c > pos) sr[h][c] = __float_as_uint(B200_NEG_INF);
+            }
+            float mx4[4] = {B200_NEG_INF, B200_NEG_INF, B200_NEG_INF, B200_NEG_INF};   // four chains: the maximum is latency-bound
 #pragma unroll
             for (int h = 0; h < 2; ++h)
 #pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    float s = __uint_as_float(sr[h][c]);
-                    if (diag && k0 + 32 * h + c > pos) s = B200_NEG_INF;
-                    sr[h][c] = __float_as_uint(s);
-                    mx = fmaxf(mx, s);
-                }
+                for (int c = 0; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[h][c]));
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             // lazy rescale: only when some row of the warp outgrew its reference maximum
             const bool grow = mx > m_ref + RESCALE_GAP || (m_ref == B200_NEG_INF && mx != B200_NEG_INF);
             if (__any_sync(0xffffffffu, grow)) {
@@ -262,6 +268,7 @@ __global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
             const float mref_safe = m_ref == B200_NEG_INF ? 0.0f : m_ref;
             if (j >= 2) mbar_wait(&p_free[j & 1], (uint32_t) (((j >> 1) - 1) & 1), a.status);   // P buffer no longer read
             unsigned char * prow = smem + SM_P + (j & 1) * P_BYTES + r * 16;
+            float l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int h = 0; h < 2; ++h)
 #pragma unroll
@@ -269,16 +276,16 @@ __global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
                     uint32_t w4[4];
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        const float s0 = __uint_as_float(sr[h][c8 * 8 + 2 * e]), s1 = __uint_as_float(sr[h][c8 * 8 + 2 * e + 1]);
-                        const __half2 p2 = __floats2half2_rn(s0 == B200_NEG_INF ? 0.0f : ex2f(s0 - mref_safe),
-                                                             s1 == B200_NEG_INF ? 0.0f : ex2f(s1 - mref_safe));
-                        const float2 pf = __half22float2(p2);
-                        l += pf.x + pf.y;
-                        w4[e] = *reinterpret_cast<const uint32_t *>(&p2);
+                        // ex2(-inf) = 0: masked keys need no special case (mref_safe is finite)
+                        const float p0 = ex2f(__uint_as_float(sr[h][c8 * 8 + 2 * e]) - mref_safe);
+                        const float p1 = ex2f(__uint_as_float(sr[h][c8 * 8 + 2 * e + 1]) - mref_safe);
+                        l4[e] += p0 + p1;
+                        w4[e] = pack_h2(p0, p1);
                     }
                     // key chunk kc = 4 h + c8 of the K-major P image: byte = kc * 2048 + row * 16
                     *reinterpret_cast<uint4 *>(prow + (4 * h + c8) * 2048) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
                 }
+            l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
             umma::fence_async_smem();
             umma::fence_before_sync();
             mbar_arrive(&p_full[j & 1]);
