@@ -131,6 +131,24 @@ int b200_attn_dec2_reload_env(void);
  * Each row's result depends only on its own keys and on chunk_keys, never on the other rows of the call. */
 int b200_attn_decode_slots(const float *q, const b200_kv_cache *c, float *out, const float *gate, int n_slots,
                            int q_len, const int32_t *pos, int max_n, int Hq, float scale, int chunk_keys, void *stream);
+/* b200_attn_decode_slots for callers that cannot allocate device memory (no counterpart in the reference, whose decode
+ * path always owns a cudaMalloc'ed scratch, src/fast/attn_dec2.cu:503-517).  Some hosts of this library run where
+ * cudaMalloc is off the table: inside a memory pool that already owns the whole GPU, or in a real-time loop that forbids
+ * allocator calls after start-up.  This entry point calls no cudaMalloc, cudaFree or
+ * other allocating routine, ever: the split partials go to a fixed 16 MiB array that is part of the library image on
+ * every GPU that loads it.  Arguments, results and bits are those of b200_attn_decode_slots.
+ *   - Limit: n_slots * Hkv * ceil(max_n / chunk) * 6 * q_len * 258 floats must fit in 16 MiB; beyond that the call returns
+ *     B200_ERR_SCRATCH with nothing launched (raise chunk_keys, or use b200_attn_decode_slots).
+ *   - The first call on each device looks up the array's device address (with that device current); make that first call
+ *     before any stream capture begins.
+ *   - All calls on a device share the one array, which keeps the previous call's partials: nothing in it needs clearing
+ *     (each call writes every partial it later reads), but two calls that overlap on the GPU (for instance on
+ *     different streams) race on it.  Serialise them.
+ *   - A kernel-side status (bad page id, timed-out wait) of this entry point is kept in a word of its own and is not
+ *     reported by b200_last_device_status. */
+int b200_attn_decode_slots_noalloc(const float *q, const b200_kv_cache *c, float *out, const float *gate, int n_slots,
+                                   int q_len, const int32_t *pos, int max_n, int Hq, float scale, int chunk_keys,
+                                   void *stream);
 /* Same pass, but the merged result is left unnormalised for a cross-GPU sequence split:
  * part_o [rows][Hq][D] = sum exp(s - m) v, part_m / part_l [rows][Hq] the running max (natural-log units, -inf if
  * the row saw no key) and the sum.  The formula of the reference's split partials (attn_dec2.cu:404-424). */

@@ -634,11 +634,92 @@ int decode_impl(const float * q, const b200_kv_cache * c, float * out, const flo
     return launch_status(who);
 }
 
+// ---- decode / verify without any allocation --------------------------------------------------------------------
+// Same kernels as decode_impl, but the split partials live in a fixed array inside the library image instead of a
+// buffer obtained from cudaMalloc.  Every GPU that loads the library carries the array (NOALLOC_BYTES) until the
+// process exits.
+constexpr size_t NOALLOC_FLOATS = (size_t) 4 << 20;                 // 16 MiB of partials
+constexpr size_t NOALLOC_BYTES = NOALLOC_FLOATS * sizeof(float);
+static __device__ __align__(256) float g_noalloc_partials[NOALLOC_FLOATS];
+static __device__ __align__(256) unsigned g_noalloc_status[64];
+struct noalloc_dev { bool ready = false; float * partials = nullptr; unsigned * status = nullptr; };
+noalloc_dev g_noalloc[64];
+
+// In host code the two array names above are host-side handles, not device addresses: the addresses the kernels need are
+// looked up once per device, with that device current.
+int noalloc_setup(noalloc_dev *& out) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return B200_ERR_CUDA; }
+    noalloc_dev & e = g_noalloc[dev & 63];
+    if (!e.ready) {
+        void * p = nullptr, * st = nullptr;
+        cudaError_t rc = cudaGetSymbolAddress(&p, g_noalloc_partials);
+        if (rc == cudaSuccess) rc = cudaGetSymbolAddress(&st, g_noalloc_status);
+        if (rc != cudaSuccess) {
+            cudaGetLastError();
+            fprintf(stderr, "b200attn: attn_decode_slots_noalloc: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(rc));
+            return B200_ERR_CUDA;
+        }
+        e.partials = (float *) p;
+        e.status = (unsigned *) st;
+        e.ready = true;
+    }
+    out = &e;
+    return B200_OK;
+}
+
+int decode_noalloc_impl(const float * q, const b200_kv_cache * c, float * out, const float * gate, int n_slots, int q_len,
+                        const int32_t * pos, int max_n, int Hq, float scale, int chunk_keys, cudaStream_t s) {
+    const char * who = "attn_decode_slots_noalloc";
+    if (!c || !q || !out || !pos || !c->k || !c->v) B200_REFUSE(B200_ERR_SHAPE, "%s: null argument", who);
+    if (c->D != DH || Hq != GQA * c->Hkv || c->Hkv <= 0) B200_REFUSE(B200_ERR_SHAPE, "%s: unsupported shape (D=%d Hq=%d Hkv=%d)", who, c->D, Hq, c->Hkv);
+    if (c->type != B200_KV_F16 && c->type != B200_KV_Q8_0 && c->type != B200_KV_Q4_0) B200_REFUSE(B200_ERR_SHAPE, "%s: unsupported cache type %u", who, c->type);
+    if (n_slots < 1 || n_slots > 65535 || q_len < 1 || q_len > B200_MAX_QLEN) B200_REFUSE(B200_ERR_SHAPE, "%s: unsupported rows (slots=%d q_len=%d)", who, n_slots, q_len);
+    if (!aligned16(c->k) || !aligned16(c->v) || !aligned16(q) || !aligned16(out) || (gate && !aligned16(gate)) || (c->pt && c->pstride % 16))
+        B200_REFUSE(B200_ERR_SHAPE, "%s: cache base, page stride, q, out and gate must be 16-byte aligned", who);
+    if (c->pt && (c->psh < 0 || c->psh > 30)) B200_REFUSE(B200_ERR_SHAPE, "%s: bad page shift %d", who, c->psh);
+    if (max_n < 1) max_n = 1;
+    const int CH = chunk_keys > 0 ? (chunk_keys + TILE - 1) / TILE * TILE : chunk_keys < 0 ? auto_chunk((long long) n_slots * max_n / 2, c->Hkv)
+                                                                                        : (g_chunk_override > 0 ? g_chunk_override : default_chunk());
+    const int max_chunks = (max_n + CH - 1) / CH;
+    const int R = q_len * GQA;
+    const size_t units = (size_t) n_slots * c->Hkv * max_chunks;
+    const size_t need = units * R * (DH + 2);
+    if (max_chunks > 65535 * 32 || need > NOALLOC_FLOATS)
+        B200_REFUSE(B200_ERR_SCRATCH, "%s: %zu bytes of split partials needed (slots %d x kv heads %d x chunks %d x rows %d), the built-in array holds %zu; "
+                    "use a larger chunk_keys or attn_decode_slots", who, need * sizeof(float), n_slots, c->Hkv, max_chunks, R, NOALLOC_BYTES);
+    noalloc_dev * e = nullptr;
+    const int src = noalloc_setup(e);
+    if (src != B200_OK) return src;
+    dec_args a;
+    a.q = q; a.g = view_of(*c);
+    a.po = e->partials; a.pm = a.po + units * R * DH; a.pl = a.pm + units * R;
+    a.pos = pos; a.p0p = nullptr; a.p0 = 0;
+    a.q_len = q_len; a.n_slots = n_slots; a.Hq = Hq;
+    a.qscale = scale * LOG2E;
+    a.CH = CH; a.max_chunks = max_chunks; a.status = e->status;
+    const dim3 grid(max_chunks, c->Hkv, n_slots);
+    int rc;
+    if (c->type == B200_KV_F16) rc = launch_part_nt<B200_KV_F16>(a, grid, s);
+    else if (c->type == B200_KV_Q8_0) rc = launch_part_nt<B200_KV_Q8_0>(a, grid, s);
+    else rc = launch_part_nt<B200_KV_Q4_0>(a, grid, s);
+    if (rc != B200_OK) return rc;
+    decode_merge_k<<<dim3(n_slots * q_len, Hq), 64, 0, s>>>(a, gate, out, nullptr, nullptr, nullptr);
+    count_launch(2);
+    return launch_status(who);
+}
+
 }  // namespace b200
 
 using namespace b200;
 
 extern "C" {
+
+// Batched decode / verify for callers that must not allocate device memory.  See include/b200attn.h.
+int b200_attn_decode_slots_noalloc(const float * q, const b200_kv_cache * c, float * out, const float * gate, int n_slots,
+                                   int q_len, const int32_t * pos, int max_n, int Hq, float scale, int chunk_keys, void * stream) {
+    return decode_noalloc_impl(q, c, out, gate, n_slots, q_len, pos, max_n, Hq, scale, chunk_keys, (cudaStream_t) stream);
+}
 
 int b200_attn_chunk_keys(void) { return g_chunk_override > 0 ? g_chunk_override : default_chunk(); }
 

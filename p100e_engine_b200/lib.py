@@ -55,6 +55,7 @@ SIGNATURES = {
     "b200_attn_dec2_set_nsplit": (None, [I]),
     "b200_attn_dec2_reload_env": (I, []),
     "b200_attn_decode_slots": (I, [P, KVP, P, P, I, I, P, I, I, F, I, P]),
+    "b200_attn_decode_slots_noalloc": (I, [P, KVP, P, P, I, I, P, I, I, F, I, P]),
     "b200_attn_decode_slots_partial": (I, [P, KVP, P, P, P, I, I, P, I, I, F, I, P]),
     "b200_attn_merge_gate": (I, [P, P, P, I, I, I, P, P, P]),
     "b200_attn_chunk_keys": (I, []),
