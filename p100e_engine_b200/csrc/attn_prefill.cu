@@ -104,6 +104,9 @@ struct pf_args {
     unsigned * status;
 };
 
+// 1 / (1 + 2^(-g log2 e)) with the hardware exponential and reciprocal (relative error ~1e-7 against expf and an IEEE divide)
+__device__ __forceinline__ float fast_sigmoid(float g) { return __fdividef(1.0f, 1.0f + ex2f(-g * LOG2E_PF)); }
+
 __device__ __forceinline__ void mbar_arrive(uint64_t * bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -135,19 +138,36 @@ __global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
         mbar_fence_init();
     }
     if (warp == 0) umma::tmem_alloc(tbase_p, 512);
-    // Q rows -> f16, scaled, K-major canonical image: byte(row, d) = (d/8)*2048 + row*16 + (d%8)*2
-    for (int i = tid; i < BM * 32; i += NTHR_PF) {
-        const int r = i & (BM - 1), dc = i >> 7;
-        const int n = n0 + r;
-        uint4 o = make_uint4(0, 0, 0, 0);
-        if (n < R) {
-            const int t = n / GQA, hh = n - t * GQA;
-            const float4 * src = reinterpret_cast<const float4 *>(a.q + ((size_t) t * a.Hq + hk * GQA + hh) * DH + dc * 8);
-            const float4 x = src[0], y = src[1];
-            const float s = a.qscale;
-            o = make_uint4(pack_h2(x.x * s, x.y * s), pack_h2(x.z * s, x.w * s), pack_h2(y.x * s, y.y * s), pack_h2(y.z * s, y.w * s));
+    // Q rows -> f16, scaled, K-major canonical image: byte(row, d) = (d/8)*2048 + row*16 + (d%8)*2.
+    // Loads are issued in batches of 8 chunks per thread before any conversion (the prologue is latency-bound otherwise).
+    {
+        constexpr int QB = 8;
+        for (int i0 = tid; i0 < BM * 32; i0 += NTHR_PF * QB) {
+            float4 x[QB], y[QB];
+#pragma unroll
+            for (int u = 0; u < QB; ++u) {
+                const int i = i0 + u * NTHR_PF;
+                const int r = i & (BM - 1), dc = i >> 7, n = n0 + r;
+                x[u] = y[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (i < BM * 32 && n < R) {
+                    const int t = n / GQA, hh = n - t * GQA;
+                    const float4 * src = reinterpret_cast<const float4 *>(a.q + ((size_t) t * a.Hq + hk * GQA + hh) * DH + dc * 8);
+                    x[u] = __ldg(src);
+                    y[u] = __ldg(src + 1);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < QB; ++u) {
+                const int i = i0 + u * NTHR_PF;
+                if (i < BM * 32) {
+                    const int r = i & (BM - 1), dc = i >> 7;
+                    const float s = a.qscale;
+                    *reinterpret_cast<uint4 *>(smem + SM_Q + dc * 2048 + r * 16) =
+                        make_uint4(pack_h2(x[u].x * s, x[u].y * s), pack_h2(x[u].z * s, x[u].w * s), pack_h2(y[u].x * s, y[u].y * s),
+                                   pack_h2(y[u].z * s, y[u].w * s));
+                }
+            }
         }
-        *reinterpret_cast<uint4 *>(smem + SM_Q + dc * 2048 + r * 16) = o;
     }
     umma::fence_async_smem();
     umma::fence_before_sync();
@@ -156,6 +176,15 @@ __global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
     const uint32_t tb = *tbase_p;
     const uint32_t t_S = tb, t_O = tb + 2 * BN;   // S double-buffered at columns 0 and 64, O behind them
 
+    if (warp >= 4 && a.gate && (lane & 15) != 0) {
+        // idle lanes of the producer and MMA warps pull this CTA's gate rows (contiguous per token: 6 heads x 1 KB) into L2
+        const int t_first = n0 / GQA;
+        const char * g0 = reinterpret_cast<const char *>(a.gate + ((size_t) t_first * a.Hq + hk * GQA) * DH);
+        const int idx = (warp - 4) * 30 + lane - 1 - (lane > 16);
+        for (int t = t_first; t <= t_last; ++t)
+            for (int ln = idx; ln < GQA * DH * 4 / 128; ln += 60)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(g0 + (size_t) (t - t_first) * a.Hq * DH * 4 + ln * 128));
+    }
     if (warp == 4) {
         // ---------------- producer: one bulk copy per image; K (lane 0) and V (lane 16) rings run independently ----------------
         const unsigned char * src = a.tiles + (size_t) hk * a.n_tiles * (2 * IMG);
@@ -294,26 +323,51 @@ __global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
         mbar_wait(o_done, 0, a.status);
         umma::fence_after_sync();
         const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-        const int hh = n - t_row * GQA;
-        const size_t orow = ((size_t) t_row * a.Hq + hk * GQA + hh) * DH;
+        // Each warp owns the 32 rows of its tensor-memory lanes.  A 32-column slab of O goes through a private
+        // shared-memory tile (the Q image is dead by now) so that global accesses run along rows: 8 lanes cover the 128
+        // bytes of one row, a warp instruction touches 4 rows.
+        float * tile = reinterpret_cast<float *>(smem + SM_Q) + warp * (32 * 33);
+        const int sub = lane >> 3, col = 4 * (lane & 7);
+        size_t orow[8];
+        bool live[8];
+#pragma unroll
+        for (int q8 = 0; q8 < 8; ++q8) {
+            const int nr = n0 + warp * 32 + 4 * q8 + sub;
+            const int tr = nr / GQA, hr = nr - tr * GQA;
+            live[q8] = nr < R;
+            orow[q8] = ((size_t) tr * a.Hq + hk * GQA + hr) * DH + col;
+        }
+        float4 gn[8];   // gate values of the next slab, requested one slab ahead
+#pragma unroll
+        for (int q8 = 0; q8 < 8; ++q8)
+            gn[q8] = (a.gate && live[q8]) ? __ldg(reinterpret_cast<const float4 *>(a.gate + orow[q8])) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 1
         for (int c0 = 0; c0 < DH; c0 += 32) {
+            float4 gv[8];
+#pragma unroll
+            for (int q8 = 0; q8 < 8; ++q8) {
+                gv[q8] = gn[q8];
+                if (a.gate && live[q8] && c0 + 32 < DH) gn[q8] = __ldg(reinterpret_cast<const float4 *>(a.gate + orow[q8] + c0 + 32));
+            }
             uint32_t o[32];
             umma::tmem_ld32(t_O + lane_off + c0, o);
             umma::tmem_ld_wait();
-            if (n < R) {
 #pragma unroll
-                for (int c = 0; c < 32; c += 4) {
-                    float4 y = make_float4(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv,
-                                           __uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
+            for (int c = 0; c < 32; ++c) tile[lane * 33 + c] = __uint_as_float(o[c]) * inv;
+            __syncwarp();
+#pragma unroll
+            for (int q8 = 0; q8 < 8; ++q8) {
+                const int rl = 4 * q8 + sub;
+                if (live[q8]) {
+                    float4 y = make_float4(tile[rl * 33 + col], tile[rl * 33 + col + 1], tile[rl * 33 + col + 2], tile[rl * 33 + col + 3]);
                     if (a.gate) {
-                        const float4 gv = *reinterpret_cast<const float4 *>(a.gate + orow + c0 + c);
-                        y.x *= 1.0f / (1.0f + expf(-gv.x)); y.y *= 1.0f / (1.0f + expf(-gv.y));
-                        y.z *= 1.0f / (1.0f + expf(-gv.z)); y.w *= 1.0f / (1.0f + expf(-gv.w));
+                        y.x *= fast_sigmoid(gv[q8].x); y.y *= fast_sigmoid(gv[q8].y);
+                        y.z *= fast_sigmoid(gv[q8].z); y.w *= fast_sigmoid(gv[q8].w);
                     }
-                    *reinterpret_cast<float4 *>(a.out + orow + c0 + c) = y;
+                    *reinterpret_cast<float4 *>(a.out + orow[q8] + c0) = y;
                 }
             }
+            __syncwarp();
         }
     }
     umma::fence_before_sync();
