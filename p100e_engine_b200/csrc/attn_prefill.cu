@@ -31,10 +31,10 @@ constexpr int NTHR_PF = 192;            // 4 softmax warps + producer + MMA issu
 constexpr float LOG2E_PF = 1.4426950408889634f;
 constexpr float RESCALE_GAP = 8.0f;     // rescale O when a row maximum grows by more than this (log2 units)
 
-constexpr int SM_Q = 0;
-constexpr int SM_K = SM_Q + Q_BYTES;            // 2 stages
-constexpr int SM_V = SM_K + 2 * IMG;            // 2 stages
-constexpr int SM_P = SM_V + 2 * IMG;            // 2 buffers
+constexpr int NSTG = 3;                 // K and V ring depth (Q lives in tensor memory, not in shared memory)
+constexpr int SM_K = 0;                         // NSTG stages
+constexpr int SM_V = SM_K + NSTG * IMG;         // NSTG stages
+constexpr int SM_P = SM_V + NSTG * IMG;         // 2 buffers
 constexpr int SM_BAR = SM_P + 2 * P_BYTES;      // mbarriers + tmem base
 constexpr int SM_TOTAL = SM_BAR + 256;
 
@@ -114,9 +114,9 @@ __device__ __forceinline__ void mbar_arrive(uint64_t * bar) {
 __global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
     extern __shared__ __align__(1024) unsigned char smem[];
     uint64_t * bars = reinterpret_cast<uint64_t *>(smem + SM_BAR);
-    uint64_t * k_full = bars, * k_free = bars + 2, * v_full = bars + 4, * v_free = bars + 6, * s_full = bars + 8,
-             * s_free = bars + 10, * p_full = bars + 12, * p_free = bars + 14, * o_done = bars + 16;
-    uint32_t * tbase_p = reinterpret_cast<uint32_t *>(bars + 18);
+    uint64_t * k_full = bars, * k_free = bars + 4, * v_full = bars + 8, * v_free = bars + 12, * s_full = bars + 16,
+             * s_free = bars + 18, * p_full = bars + 20, * p_free = bars + 22, * o_done = bars + 24, * q_ready = bars + 25;
+    uint32_t * tbase_p = reinterpret_cast<uint32_t *>(bars + 26);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int mtile = (int) gridDim.x - 1 - (int) blockIdx.x;   // heaviest (latest rows) first
@@ -128,54 +128,52 @@ __global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
     const int ntiles = (n_keys_vis + BN - 1) / BN;
 
     if (tid == 0) {
-        for (int b = 0; b < 2; ++b) {
+        for (int b = 0; b < NSTG; ++b) {
             mbar_init(&k_full[b], 1); mbar_init(&k_free[b], 1);
             mbar_init(&v_full[b], 1); mbar_init(&v_free[b], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
             mbar_init(&s_full[b], 1); mbar_init(&s_free[b], 128);
             mbar_init(&p_full[b], 128); mbar_init(&p_free[b], 1);
         }
         mbar_init(o_done, 1);
+        mbar_init(q_ready, 1);
         mbar_fence_init();
     }
     if (warp == 0) umma::tmem_alloc(tbase_p, 512);
-    // Q rows -> f16, scaled, K-major canonical image: byte(row, d) = (d/8)*2048 + row*16 + (d%8)*2.
-    // Loads are issued in batches of 8 chunks per thread before any conversion (the prologue is latency-bound otherwise).
-    {
-        constexpr int QB = 8;
-        for (int i0 = tid; i0 < BM * 32; i0 += NTHR_PF * QB) {
-            float4 x[QB], y[QB];
-#pragma unroll
-            for (int u = 0; u < QB; ++u) {
-                const int i = i0 + u * NTHR_PF;
-                const int r = i & (BM - 1), dc = i >> 7, n = n0 + r;
-                x[u] = y[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                if (i < BM * 32 && n < R) {
-                    const int t = n / GQA, hh = n - t * GQA;
-                    const float4 * src = reinterpret_cast<const float4 *>(a.q + ((size_t) t * a.Hq + hk * GQA + hh) * DH + dc * 8);
-                    x[u] = __ldg(src);
-                    y[u] = __ldg(src + 1);
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < QB; ++u) {
-                const int i = i0 + u * NTHR_PF;
-                if (i < BM * 32) {
-                    const int r = i & (BM - 1), dc = i >> 7;
-                    const float s = a.qscale;
-                    *reinterpret_cast<uint4 *>(smem + SM_Q + dc * 2048 + r * 16) =
-                        make_uint4(pack_h2(x[u].x * s, x[u].y * s), pack_h2(x[u].z * s, x[u].w * s), pack_h2(y[u].x * s, y[u].y * s),
-                                   pack_h2(y[u].z * s, y[u].w * s));
-                }
-            }
-        }
-    }
     umma::fence_async_smem();
     umma::fence_before_sync();
     __syncthreads();
     umma::fence_after_sync();
     const uint32_t tb = *tbase_p;
-    const uint32_t t_S = tb, t_O = tb + 2 * BN;   // S double-buffered at columns 0 and 64, O behind them
+    const uint32_t t_S = tb, t_O = tb + 2 * BN, t_Q = tb + 2 * BN + DH;   // S x2 at columns 0 / 64, O at 128..383, Q (f16 pairs) at 384..511
 
+    if (warp < 4) {
+        // Q rows -> f16, scaled by softmax scale * log2(e), into tensor memory as the A operand of Q K^T: thread = row =
+        // lane, column c holds dims 2c, 2c+1.  64 dims per slab: 16 loads in flight per thread.
+        const int n = n0 + tid;
+        const uint32_t lane_off = (uint32_t) (warp * 32) << 16;
+        const float4 * src = nullptr;
+        if (n < R) {
+            const int t = n / GQA, hh = n - t * GQA;
+            src = reinterpret_cast<const float4 *>(a.q + ((size_t) t * a.Hq + hk * GQA + hh) * DH);
+        }
+#pragma unroll 1
+        for (int d0 = 0; d0 < DH; d0 += 64) {
+            float4 x[16];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) x[u] = src ? __ldg(src + d0 / 4 + u) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            uint32_t w[32];
+            const float sc = a.qscale;
+#pragma unroll
+            for (int u = 0; u < 16; ++u) { w[2 * u] = pack_h2(x[u].x * sc, x[u].y * sc); w[2 * u + 1] = pack_h2(x[u].z * sc, x[u].w * sc); }
+            umma::tmem_st32(t_Q + lane_off + d0 / 2, w);
+        }
+        umma::tmem_st_wait();
+        umma::fence_before_sync();
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // the four softmax warps: every Q row is in place
+        if (tid == 0) mbar_arrive(q_ready);
+    }
     if (warp >= 4 && a.gate && (lane & 15) != 0) {
         // idle lanes of the producer and MMA warps pull this CTA's gate rows (contiguous per token: 6 heads x 1 KB) into L2
         const int t_first = n0 / GQA;
@@ -190,15 +188,15 @@ __global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
         const unsigned char * src = a.tiles + (size_t) hk * a.n_tiles * (2 * IMG);
         if (lane == 0) {
             for (int j = 0; j < ntiles; ++j) {
-                const int s = j & 1;
-                if (j >= 2) mbar_wait(&k_free[s], (uint32_t) (((j >> 1) - 1) & 1), a.status);   // Q K^T of tile j-2 has read the stage
+                const int s = j % NSTG;
+                if (j >= NSTG) mbar_wait(&k_free[s], (uint32_t) ((j / NSTG - 1) & 1), a.status);   // Q K^T of tile j-NSTG has read the stage
                 mbar_expect_tx(&k_full[s], IMG);
                 bulk_g2s(smem + SM_K + s * IMG, src + (size_t) j * (2 * IMG), IMG, &k_full[s]);
             }
         } else if (lane == 16) {
             for (int j = 0; j < ntiles; ++j) {
-                const int s = j & 1;
-                if (j >= 2) mbar_wait(&v_free[s], (uint32_t) (((j >> 1) - 1) & 1), a.status);   // P V of tile j-2 has read the stage
+                const int s = j % NSTG;
+                if (j >= NSTG) mbar_wait(&v_free[s], (uint32_t) ((j / NSTG - 1) & 1), a.status);   // P V of tile j-NSTG has read the stage
                 mbar_expect_tx(&v_full[s], IMG);
                 bulk_g2s(smem + SM_V + s * IMG, src + (size_t) j * (2 * IMG) + IMG, IMG, &v_full[s]);
             }
@@ -208,33 +206,33 @@ __global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
         if (lane == 0) {
             constexpr uint32_t id_qk = umma::idesc_f16(BM, BN, false, false);   // S[128 x 64] = Q (K-major) * K^T (K-major)
             constexpr uint32_t id_pv = umma::idesc_f16(BM, DH, false, true);    // O[128 x 256] += P (K-major) * V (MN-major)
-            const uint32_t q_s = smem_u32(smem + SM_Q);
             auto issue_qk = [&](int j) {
-                const int b = j & 1;
-                mbar_wait(&k_full[b], (uint32_t) ((j >> 1) & 1), a.status);
+                const int b = j & 1, st = j % NSTG;
+                mbar_wait(&k_full[st], (uint32_t) ((j / NSTG) & 1), a.status);
                 if (j >= 2) mbar_wait(&s_free[b], (uint32_t) (((j >> 1) - 1) & 1), a.status);   // softmax of tile j-2 holds S in registers
                 umma::fence_after_sync();
-                const uint32_t k_s = smem_u32(smem + SM_K + b * IMG);
+                const uint32_t k_s = smem_u32(smem + SM_K + st * IMG);
 #pragma unroll 4
                 for (int ks = 0; ks < DH / 16; ++ks)
-                    umma::mma_ss(t_S + b * BN, umma::smem_desc(q_s + ks * 2 * 2048, 2048, 128),
-                                 umma::smem_desc(k_s + ks * 2 * 1024, 1024, 128), id_qk, ks > 0);
+                    umma::mma_ts(t_S + b * BN, t_Q + ks * 8, umma::smem_desc(k_s + ks * 2 * 1024, 1024, 128), id_qk, ks > 0);   // Q from tensor memory
                 umma::commit(&s_full[b]);
-                umma::commit(&k_free[b]);
+                umma::commit(&k_free[st]);
             };
+            mbar_wait(q_ready, 0, a.status);
+            umma::fence_after_sync();
             issue_qk(0);
             for (int j = 0; j < ntiles; ++j) {
                 if (j + 1 < ntiles) issue_qk(j + 1);
-                const int b = j & 1;
-                mbar_wait(&v_full[b], (uint32_t) ((j >> 1) & 1), a.status);
+                const int b = j & 1, st = j % NSTG;
+                mbar_wait(&v_full[st], (uint32_t) ((j / NSTG) & 1), a.status);
                 mbar_wait(&p_full[b], (uint32_t) ((j >> 1) & 1), a.status);
                 umma::fence_after_sync();
-                const uint32_t p_s = smem_u32(smem + SM_P + b * P_BYTES), v_s = smem_u32(smem + SM_V + b * IMG);
+                const uint32_t p_s = smem_u32(smem + SM_P + b * P_BYTES), v_s = smem_u32(smem + SM_V + st * IMG);
 #pragma unroll
                 for (int ks = 0; ks < BN / 16; ++ks)   // V image: MN-major, key groups of 8 contiguous (LBO 128), dim groups 1024 apart
                     umma::mma_ss(t_O, umma::smem_desc(p_s + ks * 2 * 2048, 2048, 128), umma::smem_desc(v_s + ks * 2 * 128, 128, 1024),
                                  id_pv, (j > 0 || ks > 0) ? 1u : 0u);
-                umma::commit(&v_free[b]);
+                umma::commit(&v_free[st]);
                 umma::commit(&p_free[b]);
             }
             umma::commit(o_done);
@@ -324,9 +322,9 @@ __global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
         umma::fence_after_sync();
         const float inv = l > 0.0f ? 1.0f / l : 0.0f;
         // Each warp owns the 32 rows of its tensor-memory lanes.  A 32-column slab of O goes through a private
-        // shared-memory tile (the Q image is dead by now) so that global accesses run along rows: 8 lanes cover the 128
+        // shared-memory tile (the P buffers are dead by now) so that global accesses run along rows: 8 lanes cover the 128
         // bytes of one row, a warp instruction touches 4 rows.
-        float * tile = reinterpret_cast<float *>(smem + SM_Q) + warp * (32 * 33);
+        float * tile = reinterpret_cast<float *>(smem + SM_P) + warp * (32 * 33);
         const int sub = lane >> 3, col = 4 * (lane & 7);
         size_t orow[8];
         bool live[8];
