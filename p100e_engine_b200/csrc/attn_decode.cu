@@ -37,7 +37,7 @@ constexpr float PSHIFT = 8.0f;        // P (and l) are kept times 2^8 inside the
 template <uint32_t KT> struct traits {
     static constexpr int HB = head_bytes(KT);                       // bytes of a head row in the cache
     static constexpr int SROW = KT == B200_KV_F16 ? HB + 16 : HB;   // bytes per key row in shared memory (= 4 mod 32 words)
-    static constexpr int STAGE = 2 * TILE * SROW;                   // K rows then V rows
+    static constexpr int SLOT = TILE * SROW;                        // one ring slot: the K rows or the V rows of a tile
     static constexpr bool SCALED = KT != B200_KV_F16;
 };
 
@@ -85,7 +85,7 @@ template <int HI> __device__ __forceinline__ uint32_t cvt_n4x2(uint32_t u) {
 }
 
 template <uint32_t KT, int NT>
-__global__ void __launch_bounds__(NTHR) decode_part_k(const dec_args a, const int nstage) {
+__global__ void __launch_bounds__(NTHR) decode_part_k(const dec_args a, const int nslot) {
     using TR = traits<KT>;
     constexpr int HB = TR::HB, SROW = TR::SROW;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -102,16 +102,16 @@ __global__ void __launch_bounds__(NTHR) decode_part_k(const dec_args a, const in
     const int ntiles = (k_hi - k_lo + TILE - 1) / TILE;
 
     // shared memory carve-up
-    uint64_t * full = reinterpret_cast<uint64_t *>(smem);                    // [nstage]
-    unsigned char * stg = smem + 128;                                        // nstage * STAGE
-    unsigned char * Qs = stg + (size_t) nstage * TR::STAGE;                  // [NT*8][QSTR]
+    uint64_t * full = reinterpret_cast<uint64_t *>(smem);                    // [nslot]
+    unsigned char * stg = smem + 128;                                        // nslot * SLOT
+    unsigned char * Qs = stg + (size_t) nslot * TR::SLOT;                    // [NT*8][QSTR]
     unsigned char * Ps = Qs + NT * 8 * QSTR;                                 // [NT*8][PSTR]
     unsigned char * Sd = Ps + NT * 8 * PSTR;                                 // [8][SDSTR]  V block scales, transposed
     float * wmax = reinterpret_cast<float *>(Sd + 8 * SDSTR);                // [NWARP][NT*8]
     float * wl = wmax + NWARP * NT * 8;                                      // [NWARP][NT*8]
 
     if (tid == 0) {
-        for (int s = 0; s < nstage; ++s) mbar_init(&full[s], 1);
+        for (int s = 0; s < nslot; ++s) mbar_init(&full[s], 1);
         mbar_fence_init();
     }
     // Q rows -> shared memory as f16, scaled; row r = j * 6 + hh (verify row j, head hh of the group)
@@ -132,12 +132,14 @@ __global__ void __launch_bounds__(NTHR) decode_part_k(const dec_args a, const in
     const int32_t * tab = a.g.pt ? a.g.pt + (a.g.rtab ? a.g.rtab[slot * a.q_len] : 0) : nullptr;
     const unsigned long long hoff = (unsigned long long) hk * HB;
 
-    // producer: warp 0 copies the 64 K rows and 64 V rows of tile `it` into stage it % nstage (rows past the slot's
-    // last key are replaced by that last key: always readable, and masked in the softmax)
-    auto issue = [&](int it) {
-        const int s = it % nstage;
-        unsigned char * dst = stg + (size_t) s * TR::STAGE;
-        if (lane == 0) mbar_expect_tx(&full[s], 2u * TILE * HB);
+    // producer: the K rows and the V rows of the tiles form one sequence q = 2 * tile (K), 2 * tile + 1 (V) that walks a ring
+    // of nslot half-tile slots, so a K slot is refilled as soon as its Q K^T is done.  Warp 0 copies the 64 rows of item q
+    // (rows past the slot's last key are replaced by that last key: always readable, and masked in the softmax).
+    auto issue = [&](int q) {
+        const int s = q % nslot, it = q >> 1;
+        unsigned char * dst = stg + (size_t) s * TR::SLOT;
+        const char * base = (q & 1) ? a.g.v : a.g.k;
+        if (lane == 0) mbar_expect_tx(&full[s], (uint32_t) TILE * HB);
         __syncwarp();
 #pragma unroll
         for (int rr = 0; rr < TILE / 32; ++rr) {
@@ -149,13 +151,12 @@ __global__ void __launch_bounds__(NTHR) decode_part_k(const dec_args a, const in
                 if (pg < 0) { atomicOr(a.status, ST_BAD_PAGE); off = 0; }
                 else off = (unsigned long long) pg * a.g.pstride + (unsigned long long) (p & ((1 << a.g.psh) - 1)) * a.g.rowb;
             } else off = (unsigned long long) p * a.g.rowb;
-            off += hoff;
-            bulk_g2s(dst + row * SROW, a.g.k + off, HB, &full[s]);
-            bulk_g2s(dst + (TILE + row) * SROW, a.g.v + off, HB, &full[s]);
+            bulk_g2s(dst + row * SROW, base + off + hoff, HB, &full[s]);
         }
     };
+    int next_q = 0;   // uniform in warp 0
     if (w == 0)
-        for (int it = 0; it < nstage && it < ntiles; ++it) issue(it);
+        for (; next_q < nslot && next_q < 2 * ntiles; ++next_q) issue(next_q);
 
     // per-lane row bookkeeping: this lane's score / output columns are rows 8i + 2t and 8i + 2t + 1
     int rpos[NT][2];
@@ -180,10 +181,10 @@ __global__ void __launch_bounds__(NTHR) decode_part_k(const dec_args a, const in
     const int kA = 16 * w + key_perm<KT>(g), kB = kA + 8;   // this lane's two keys (tile-relative) in the QK phase
 
     for (int it = 0; it < ntiles; ++it) {
-        const int s = it % nstage;
-        const unsigned char * Ks = stg + (size_t) s * TR::STAGE;
-        const unsigned char * Vs = Ks + TILE * SROW;
-        mbar_wait(&full[s], (uint32_t) ((it / nstage) & 1), a.status);
+        const int qk = 2 * it, qv = 2 * it + 1;
+        const unsigned char * Ks = stg + (size_t) (qk % nslot) * TR::SLOT;
+        const unsigned char * Vs = stg + (size_t) (qv % nslot) * TR::SLOT;
+        mbar_wait(&full[qk % nslot], (uint32_t) ((qk / nslot) & 1), a.status);
 
         // ---------------- S = K Q^T for the warp's 16 keys ----------------
         float S[NT][4];
@@ -269,7 +270,10 @@ __global__ void __launch_bounds__(NTHR) decode_part_k(const dec_args a, const in
                 if (g == 0) wmax[w * NT * 8 + 8 * i + 2 * t + e] = mx;
             }
         __syncthreads();   // B1: row maxima visible; every warp is done with the previous tile's PV
-        if (w == 0 && it >= 1 && it - 1 + nstage < ntiles) issue(it - 1 + nstage);
+        // items up to 2 it (this tile's K, the previous tile's V) are consumed: their slots take the items nslot ahead
+        if (w == 0)
+            for (; next_q < 2 * ntiles && next_q <= 2 * it + nslot; ++next_q) issue(next_q);
+        mbar_wait(&full[qv % nslot], (uint32_t) ((qv / nslot) & 1), a.status);   // this tile's V rows
 
         // ---------------- online softmax, P -> shared memory ----------------
         float fsc[NT][2];
@@ -550,25 +554,29 @@ float * scratch_for(cudaStream_t s, size_t floats) {
     return e->p;
 }
 
-template <uint32_t KT, int NT> size_t smem_bytes(int nstage) {
-    return 128 + (size_t) nstage * traits<KT>::STAGE + NT * 8 * (QSTR + PSTR) + 8 * SDSTR + 2 * NWARP * NT * 8 * sizeof(float);
+template <uint32_t KT, int NT> size_t smem_bytes(int nslot) {
+    return 128 + (size_t) nslot * traits<KT>::SLOT + NT * 8 * (QSTR + PSTR) + 8 * SDSTR + 2 * NWARP * NT * 8 * sizeof(float);
 }
 
 template <uint32_t KT, int NT>
 int launch_part(const dec_args & a, dim3 grid, cudaStream_t s) {
-    // deepest ring that still lets two CTAs share an SM (227 KB usable), at least 2 stages
-    int nstage = 4;
-    while (nstage > 2 && 2 * (smem_bytes<KT, NT>(nstage) + 1024) > 227 * 1024) --nstage;
-    const size_t sm = smem_bytes<KT, NT>(nstage);
+    // deepest ring (3..8 half-tile slots) that still lets three CTAs share an SM (227 KB usable); if three never fit, the
+    // deepest that lets two
+    auto fits = [](int n, int ctas) { return (size_t) ctas * (smem_bytes<KT, NT>(n) + 1024) <= (size_t) 227 * 1024; };
+    int nslot = 3;
+    const int ctas = fits(3, 3) ? 3 : 2;
+    while (nslot < 8 && fits(nslot + 1, ctas)) ++nslot;
+    const size_t sm = smem_bytes<KT, NT>(nslot);
     static bool attr_done[64] = {};   // per instantiation and device
     int dev = 0;
     cudaGetDevice(&dev);
     if (!attr_done[dev & 63]) {
         if (cudaFuncSetAttribute(decode_part_k<KT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) sm) != cudaSuccess)
             return launch_status("attn_decode (shared memory attribute)");
+        cudaFuncSetAttribute(decode_part_k<KT, NT>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         attr_done[dev & 63] = true;
     }
-    decode_part_k<KT, NT><<<grid, NTHR, sm, s>>>(a, nstage);
+    decode_part_k<KT, NT><<<grid, NTHR, sm, s>>>(a, nslot);
     return B200_OK;
 }
 
