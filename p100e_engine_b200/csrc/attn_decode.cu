@@ -26,7 +26,10 @@ namespace b200 {
 namespace {
 
 constexpr int TILE = 64;              // keys per tile
-constexpr int NWARP = 4, NTHR = NWARP * 32;
+constexpr int NWARP = 4, NTHR = NWARP * 32;   // compute warps
+constexpr int NTHR_CTA = NTHR + 32;           // + one producer warp
+__device__ __forceinline__ void bar_tile() { asm volatile("bar.sync 1, %0;" ::"n"(NTHR_CTA) : "memory"); }   // compute + producer
+__device__ __forceinline__ void bar_compute() { asm volatile("bar.sync 2, %0;" ::"n"(NTHR) : "memory"); }   // compute warps only
 constexpr int QSTR = 576;             // bytes per Q row in shared memory (256 f16 + 64: rows g, g+1 on different bank halves)
 constexpr int PSTR = 144;             // bytes per P row (64 f16 + 16)
 constexpr int SDSTR = 132;            // bytes per V-scale row (64 f16 + 4)
@@ -85,7 +88,7 @@ template <int HI> __device__ __forceinline__ uint32_t cvt_n4x2(uint32_t u) {
 }
 
 template <uint32_t KT, int NT>
-__global__ void __launch_bounds__(NTHR) decode_part_k(const dec_args a, const int nslot) {
+__global__ void __launch_bounds__(NTHR_CTA, KT == B200_KV_F16 ? 2 : 3) decode_part_k(const dec_args a, const int nslot) {
     using TR = traits<KT>;
     constexpr int HB = TR::HB, SROW = TR::SROW;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -115,7 +118,7 @@ __global__ void __launch_bounds__(NTHR) decode_part_k(const dec_args a, const in
         mbar_fence_init();
     }
     // Q rows -> shared memory as f16, scaled; row r = j * 6 + hh (verify row j, head hh of the group)
-    for (int i = tid; i < NT * 8 * (DH / 4); i += NTHR) {
+    for (int i = tid; w < NWARP && i < NT * 8 * (DH / 4); i += NTHR) {
         const int r = i / (DH / 4), d4 = (i - r * (DH / 4)) * 4;
         float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         if (r < R) {
@@ -154,9 +157,17 @@ __global__ void __launch_bounds__(NTHR) decode_part_k(const dec_args a, const in
             bulk_g2s(dst + row * SROW, base + off + hoff, HB, &full[s]);
         }
     };
-    int next_q = 0;   // uniform in warp 0
-    if (w == 0)
+    if (w == NWARP) {
+        // the producer warp fills the ring, then follows the compute warps tile by tile: when they pass the barrier of
+        // tile `it`, items up to 2 it (that tile's K, the previous tile's V) are consumed and their slots are refilled
+        int next_q = 0;
         for (; next_q < nslot && next_q < 2 * ntiles; ++next_q) issue(next_q);
+        for (int it = 0; it < ntiles; ++it) {
+            bar_tile();
+            for (; next_q < 2 * ntiles && next_q <= 2 * it + nslot; ++next_q) issue(next_q);
+        }
+        return;
+    }
 
     // per-lane row bookkeeping: this lane's score / output columns are rows 8i + 2t and 8i + 2t + 1
     int rpos[NT][2];
@@ -269,10 +280,7 @@ __global__ void __launch_bounds__(NTHR) decode_part_k(const dec_args a, const in
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
                 if (g == 0) wmax[w * NT * 8 + 8 * i + 2 * t + e] = mx;
             }
-        __syncthreads();   // B1: row maxima visible; every warp is done with the previous tile's PV
-        // items up to 2 it (this tile's K, the previous tile's V) are consumed: their slots take the items nslot ahead
-        if (w == 0)
-            for (; next_q < 2 * ntiles && next_q <= 2 * it + nslot; ++next_q) issue(next_q);
+        bar_tile();   // B1: row maxima visible; every warp is done with the previous tile's PV (the producer refills slots)
         mbar_wait(&full[qv % nslot], (uint32_t) ((qv / nslot) & 1), a.status);   // this tile's V rows
 
         // ---------------- online softmax, P -> shared memory ----------------
@@ -311,7 +319,7 @@ __global__ void __launch_bounds__(NTHR) decode_part_k(const dec_args a, const in
                 O[mt][i][0] *= fsc[i][0]; O[mt][i][1] *= fsc[i][1];
                 O[mt][i][2] *= fsc[i][0]; O[mt][i][3] *= fsc[i][1];
             }
-        __syncthreads();   // B2: P and the V scales are visible
+        bar_compute();   // B2: P and the V scales are visible
 
         // ---------------- O^T += V^T P^T for the warp's 64 output dims ----------------
 #pragma unroll
@@ -395,7 +403,7 @@ __global__ void __launch_bounds__(NTHR) decode_part_k(const dec_args a, const in
             l += __shfl_xor_sync(0xffffffffu, l, 16);
             if (g == 0) wl[w * NT * 8 + 8 * i + 2 * t + e] = l;
         }
-    __syncthreads();
+    bar_compute();
     const size_t unit = ((size_t) slot * a.g.Hkv + hk) * a.max_chunks + chunk;
     if (w == 0 && g == 0) {
 #pragma unroll
@@ -576,7 +584,7 @@ int launch_part(const dec_args & a, dim3 grid, cudaStream_t s) {
         cudaFuncSetAttribute(decode_part_k<KT, NT>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         attr_done[dev & 63] = true;
     }
-    decode_part_k<KT, NT><<<grid, NTHR, sm, s>>>(a, nslot);
+    decode_part_k<KT, NT><<<grid, NTHR_CTA, sm, s>>>(a, nslot);
     return B200_OK;
 }
 
