@@ -7,7 +7,7 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libb200attn.so")
+LIB_PATH = os.environ.get("B200ATTN_LIB") or os.path.join(HERE, "libb200attn.so")   # B200ATTN_LIB: another build of the same ABI
 
 KV_F16, KV_Q4_0, KV_Q8_0 = 1, 2, 8
 ATTN_MAX_ROWS = 8
