@@ -238,6 +238,7 @@ def p100e_ref():
         r.ref_attn_fold_scratch_bytes.argtypes = [I, I, I, I]
         r.ref_attn_fold.argtypes = [P, KP, P, I, I, I, F, P, C.c_size_t, P]
         r.ref_attn_prep.argtypes = [P, P, P, P, P, P, P, P, KP, I, I, I, I, I, I, F, F, P]
+        r.ref_attn_prep_mrope.argtypes = [P, P, P, P, P, P, P, P, KP, I, I, I, I, I, I, F, F, P, P, I, I, I, I, I]
         r.ref_sigmoid_mul.restype = None
         r.ref_sigmoid_mul.argtypes = [P, P, C.c_int64, P]
         r.ref_k_sigmoid_mul.restype = None

@@ -69,6 +69,15 @@ VIS int ref_attn_prep(const float * qg, const float * k, const float * v, const 
     F::kv_cache c = conv(r);
     return F::attn_prep(qg, k, v, qn, kn, pos, q, gate, c, p0, T, Hq, Hkv, D, n_rot, freq_base, eps, (cudaStream_t) s) ? 0 : 1;
 }
+VIS int ref_attn_prep_mrope(const float * qg, const float * k, const float * v, const float * qn, const float * kn,
+                            const int32_t * pos, float * q, float * gate, const ref_kv * r, int p0, int T, int Hq, int Hkv, int D,
+                            int n_rot, float freq_base, float eps, void * s, const int32_t * mp, int stride, int s0, int s1, int s2,
+                            int sect) {
+    F::kv_cache c = conv(r);
+    F::mrope_pos mr;
+    mr.p = mp; mr.stride = stride; mr.s0 = s0; mr.s1 = s1; mr.s2 = s2; mr.sect = sect;
+    return F::attn_prep(qg, k, v, qn, kn, pos, q, gate, c, p0, T, Hq, Hkv, D, n_rot, freq_base, eps, (cudaStream_t) s, 0, 0, 0, mr) ? 0 : 1;
+}
 VIS void ref_sigmoid_mul(float * x, const float * g, int64_t n, void * s) { F::sigmoid_mul(x, g, n, (cudaStream_t) s); }
 VIS void ref_k_sigmoid_mul(float * x, const float * g, int64_t n, void * s) { K::sigmoid_mul(x, g, n, (cudaStream_t) s); }
 VIS int ref_ew_quant(int op, const float * a, const float * b, float * y, void * qbuf, int T, int n, void * s) {
