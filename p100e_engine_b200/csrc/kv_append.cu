@@ -86,6 +86,14 @@ __global__ void __launch_bounds__(256) append_k(const float * __restrict__ k, co
 }
 
 // ------------------------------------------------------------------------------------------- attention prep ----
+// NEOX rotation of one pair.  Written with explicit roundings (one product rounded, the other fused into the add) so that
+// every kernel of this file produces the same bits whatever the surrounding code looks like; the choice of the fused product
+// is the one nvcc makes for the reference's x0*c - x1*s / x0*s + x1*c (checked bytewise against the reference kernels).
+__device__ __forceinline__ void rot_pair(float x0, float x1, float c, float sn, float & y0, float & y1) {
+    y0 = __fmaf_rn(x0, c, -__fmul_rn(x1, sn));
+    y1 = __fmaf_rn(x1, c, __fmul_rn(x0, sn));
+}
+
 __device__ __forceinline__ float butterfly_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -183,9 +191,7 @@ __global__ void prep_k(const TIN * __restrict__ qg, const TIN * __restrict__ k, 
         if constexpr (MR) theta = (float) mrope_position(mr, t, j) * powf(freq_base, -2.0f * j / n_rot);
         else theta = (float) ppos * powf(freq_base, -2.0f * j / n_rot);
         const float c = cosf(theta), sn = sinf(theta);
-        const float x0 = smr[j], x1 = smr[j + half];
-        smr[j]        = x0 * c - x1 * sn;
-        smr[j + half] = x0 * sn + x1 * c;
+        rot_pair(smr[j], smr[j + half], c, sn, smr[j], smr[j + half]);
     }
     __syncthreads();
     if (isq) {
@@ -194,6 +200,82 @@ __global__ void prep_k(const TIN * __restrict__ qg, const TIN * __restrict__ k, 
     } else {
         char * head = g.k + roff + (unsigned long long) h * head_bytes(KT, D);
         for (int bb = wid; bb < nb; bb += nw) store_block_warp<KT>(smr[bb * 32 + lane], lane, head, bb, nb);
+    }
+}
+
+// The prefill path over whole token rows (bf16 in, no norm): one block of 256 threads per token.  cos / sin of a rotary
+// pair depend on the token and the pair only, so they are computed once per token instead of once per head (same
+// expressions, same values); q rows move as 16-byte loads / 32-byte stores; the K heads are rotated in shared memory and
+// every warp then quantises 32-value blocks of K and V.  Needs n_rot % 16 == 0 and 16-byte aligned rows.
+__device__ __forceinline__ void bf16x8_to_f32(const uint4 u, float (&f)[8]) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { f[2 * e] = __uint_as_float(w[e] << 16); f[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u); }
+}
+template <uint32_t KT>
+__global__ void __launch_bounds__(256) rope_rows_k(const __nv_bfloat16 * __restrict__ qg, const __nv_bfloat16 * __restrict__ k,
+                                                   const __nv_bfloat16 * __restrict__ v, float * __restrict__ q, kv_view g, int p0,
+                                                   int Hq, int Hkv, int D, int n_rot, float freq_base, unsigned * status) {
+    extern __shared__ float smr[];   // cos[half] | sin[half] | K heads [Hkv][D]
+    const int t = blockIdx.x, i = threadIdx.x, half = n_rot / 2, lane = i & 31, wid = i >> 5, nb = D / 32;
+    float * cs = smr, * kb = smr + n_rot;
+    const int ppos = p0 + t;
+    for (int j = i; j < half; j += 256) {
+        const float theta = (float) ppos * powf(freq_base, -2.0f * j / n_rot);
+        cs[j] = cosf(theta);
+        cs[half + j] = sinf(theta);
+    }
+    for (int e = i; e < Hkv * D / 8; e += 256) {
+        float f[8];
+        bf16x8_to_f32(__ldg(reinterpret_cast<const uint4 *>(k + (size_t) t * Hkv * D) + e), f);
+        reinterpret_cast<float4 *>(kb)[2 * e] = make_float4(f[0], f[1], f[2], f[3]);
+        reinterpret_cast<float4 *>(kb)[2 * e + 1] = make_float4(f[4], f[5], f[6], f[7]);
+    }
+    __syncthreads();
+    if (qg) {
+        const int PI = half / 8, IT = PI + (D - n_rot) / 8;   // per head: items of 8 rotary pairs, then items of 8 plain values
+        for (int it = i; it < Hq * IT; it += 256) {
+            const int h = it / IT, r = it - h * IT;
+            const __nv_bfloat16 * src = qg + ((size_t) t * Hq + h) * D;
+            float * dst = q + ((size_t) t * Hq + h) * D;
+            if (r < PI) {
+                const int d0 = r * 8;
+                float a[8], b[8], y0[8], y1[8];
+                bf16x8_to_f32(__ldg(reinterpret_cast<const uint4 *>(src + d0)), a);
+                bf16x8_to_f32(__ldg(reinterpret_cast<const uint4 *>(src + d0 + half)), b);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float c = cs[d0 + e], sn = cs[half + d0 + e];
+                    rot_pair(a[e], b[e], c, sn, y0[e], y1[e]);
+                }
+                reinterpret_cast<float4 *>(dst + d0)[0] = make_float4(y0[0], y0[1], y0[2], y0[3]);
+                reinterpret_cast<float4 *>(dst + d0)[1] = make_float4(y0[4], y0[5], y0[6], y0[7]);
+                reinterpret_cast<float4 *>(dst + d0 + half)[0] = make_float4(y1[0], y1[1], y1[2], y1[3]);
+                reinterpret_cast<float4 *>(dst + d0 + half)[1] = make_float4(y1[4], y1[5], y1[6], y1[7]);
+            } else {
+                const int d0 = n_rot + (r - PI) * 8;
+                float a[8];
+                bf16x8_to_f32(__ldg(reinterpret_cast<const uint4 *>(src + d0)), a);
+                reinterpret_cast<float4 *>(dst + d0)[0] = make_float4(a[0], a[1], a[2], a[3]);
+                reinterpret_cast<float4 *>(dst + d0)[1] = make_float4(a[4], a[5], a[6], a[7]);
+            }
+        }
+    }
+    for (int e = i; e < Hkv * half; e += 256) {
+        const int h = e / half, j = e - h * half;
+        const float c = cs[j], sn = cs[half + j];
+        rot_pair(kb[h * D + j], kb[h * D + j + half], c, sn, kb[h * D + j], kb[h * D + j + half]);
+    }
+    __syncthreads();
+    const int row = p0 + t;
+    const int32_t * tab = kv_tab(g, t);
+    if (tab && tab[row >> g.psh] < 0) { if (i == 0) atomicOr(status, ST_BAD_PAGE); return; }
+    const unsigned long long roff = kv_off_tab(g, tab, row);
+    for (int bb = wid; bb < Hkv * nb; bb += 8) {
+        const int h = bb / nb, b = bb - h * nb;
+        const unsigned long long ho = roff + (unsigned long long) h * head_bytes(KT, D);
+        store_block_warp<KT>(kb[bb * 32 + lane], lane, g.k + ho, b, nb);
+        store_block_warp<KT>(__bfloat162float(v[(size_t) t * Hkv * D + bb * 32 + lane]), lane, g.v + ho, b, nb);
     }
 }
 
@@ -401,6 +483,19 @@ int b200_rope_append_bf16(const uint16_t * q, const uint16_t * k, const uint16_t
     if (!type_ok(c->type) || !c->k || c->D != D || c->Hkv != Hkv || D % 128 || D > 1024 || n_rot > D || n_rot % 2 || p0 < 0 ||
         (!c->pt && p0 + T > c->n_ctx) || (q_out && !aligned16(q_out)))
         B200_REFUSE(B200_ERR_SHAPE, "rope_append_bf16: unsupported shape / cache (D=%d Hkv=%d n_rot=%d p0=%d)", D, Hkv, n_rot, p0);
+    const size_t smem = ((size_t) n_rot + (size_t) Hkv * D) * sizeof(float);
+    if (n_rot % 16 == 0 && smem <= 48 * 1024 && aligned16(q) && aligned16(k) && aligned16(v)) {   // whole-row kernel
+        unsigned * st = device_status_word();
+        if (!st) return B200_ERR_CUDA;
+        const kv_view g = view_of(*c);
+        const __nv_bfloat16 * qb = (const __nv_bfloat16 *) q, * kb = (const __nv_bfloat16 *) k, * vb = (const __nv_bfloat16 *) v;
+        cudaStream_t s = (cudaStream_t) stream;
+        if (c->type == B200_KV_F16) rope_rows_k<B200_KV_F16><<<T, 256, smem, s>>>(qb, kb, vb, q_out, g, p0, Hq, Hkv, D, n_rot, freq_base, st);
+        else if (c->type == B200_KV_Q8_0) rope_rows_k<B200_KV_Q8_0><<<T, 256, smem, s>>>(qb, kb, vb, q_out, g, p0, Hq, Hkv, D, n_rot, freq_base, st);
+        else rope_rows_k<B200_KV_Q4_0><<<T, 256, smem, s>>>(qb, kb, vb, q_out, g, p0, Hq, Hkv, D, n_rot, freq_base, st);
+        count_launch();
+        return launch_status("rope_append_bf16");
+    }
     return prep_launch<__nv_bfloat16, false, false>((const __nv_bfloat16 *) q, (const __nv_bfloat16 *) k, (const __nv_bfloat16 *) v,
                                                     nullptr, nullptr, nullptr, q_out, nullptr, c, p0, T, Hq, Hkv, D, n_rot,
                                                     freq_base, 0.0f, (cudaStream_t) stream, Hq * D, Hkv * D, Hkv * D, nullptr);

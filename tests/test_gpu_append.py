@@ -203,3 +203,32 @@ def test_rope_append_bf16_vs_oracle(cuda, lib):
     assert np.array_equal(c.v.cpu().numpy(), oc.v)
     assert (c.k.cpu().numpy() != oc.k).mean() < 1e-2
     np.testing.assert_allclose(q_out.cpu().numpy(), qr, rtol=1e-5, atol=2e-4 + 1.2e-7 * (p0 + T))
+
+
+@pytest.mark.parametrize("tname", ["f16", "q8_0", "q4_0"])
+def test_rope_append_bf16_row_kernel_equals_head_kernel(cuda, lib, tname):
+    """16-byte aligned inputs take the one-block-per-token kernel, inputs shifted by one element the one-block-per-head
+    kernel: same expressions, so the cache bytes and the rotated q must be identical"""
+    import torch
+    from p100e_engine_b200 import fast
+    T, p0, n_rot, base = 257, 1000, 64, 1e7
+    kt = TYPES[tname]
+    outs = []
+    for shift in (0, 1):
+        bufs = []
+        for seed, heads in ((70, HQ), (71, HKV), (72, HKV)):
+            x = torch.from_numpy(util.rng_normal(seed, (T, heads, D))).to(torch.bfloat16)
+            flat = torch.zeros(x.numel() + 8, dtype=torch.bfloat16, device=cuda)
+            flat[shift:shift + x.numel()] = x.reshape(-1).to(cuda)
+            bufs.append(flat[shift:shift + x.numel()].view(T, heads, D))
+        assert (bufs[0].data_ptr() % 16 == 0) == (shift == 0)
+        c = fast.kv_alloc(kt, 2048, HKV, D)
+        q_out = torch.zeros(T, HQ, D, device=cuda)
+        assert fast.rope_append_bf16(bufs[0], bufs[1], bufs[2], q_out, c, p0, T, HQ, HKV, D, n_rot, base)
+        torch.cuda.synchronize()
+        assert fast.device_status() == 0
+        rowb = orc.row_bytes(kt, HKV, D)   # only the appended rows are defined
+        rows = slice(p0 * rowb, (p0 + T) * rowb)
+        outs.append((c.k.cpu().numpy().reshape(-1)[rows].copy(), c.v.cpu().numpy().reshape(-1)[rows].copy(), q_out.cpu().numpy().copy()))
+    for a, b in zip(outs[0], outs[1]):
+        assert np.array_equal(a.view(np.uint8), b.view(np.uint8))
