@@ -18,7 +18,9 @@
 // Reference counterpart: dec2_k / attn_decode2 (src/fast/attn_dec2.cu:210-530), fp32 FFMA on sm_60.
 #include "common.cuh"
 
+#include <cuda.h>   // CUtensorMap and its enums only: the encoder is looked up at run time, nothing links against libcuda
 #include <algorithm>
+#include <cstring>
 #include <cstdlib>
 #include <mutex>
 
@@ -70,7 +72,16 @@ struct dec_args {
     float qscale;                         // softmax scale * log2(e)
     int CH, max_chunks;
     unsigned * status;
+    int n_ctx;                            // rows of a contiguous cache
+    int tiled;                            // set by the launcher: whole tiles are fetched through the tensor maps
 };
+
+// One tiled copy (TMA unit) of a box of a rank-3 tensor into shared memory, completion counted in bytes on an mbarrier.
+// x is in 16-bit elements and x * 2 must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_box3(void * dst, const CUtensorMap * map, int x, int y, int z, uint64_t * bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
+}
 
 __device__ __forceinline__ int row_pos(const dec_args & a, int slot, int j) {
     const int r = slot * a.q_len + j;
@@ -88,7 +99,8 @@ template <int HI> __device__ __forceinline__ uint32_t cvt_n4x2(uint32_t u) {
 }
 
 template <uint32_t KT, int NT>
-__global__ void __launch_bounds__(NTHR_CTA, KT == B200_KV_F16 ? 2 : 3) decode_part_k(const dec_args a, const int nslot) {
+__global__ void __launch_bounds__(NTHR_CTA, KT == B200_KV_F16 ? 2 : 3)
+decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV) {
     using TR = traits<KT>;
     constexpr int HB = TR::HB, SROW = TR::SROW;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -136,12 +148,31 @@ __global__ void __launch_bounds__(NTHR_CTA, KT == B200_KV_F16 ? 2 : 3) decode_pa
     const unsigned long long hoff = (unsigned long long) hk * HB;
 
     // producer: the K rows and the V rows of the tiles form one sequence q = 2 * tile (K), 2 * tile + 1 (V) that walks a ring
-    // of nslot half-tile slots, so a K slot is refilled as soon as its Q K^T is done.  Warp 0 copies the 64 rows of item q
-    // (rows past the slot's last key are replaced by that last key: always readable, and masked in the softmax).
+    // of nslot half-tile slots, so a K slot is refilled as soon as its Q K^T is done.  A tile that lies inside the slot's
+    // keys is one tiled copy through the cache's tensor map (box = 64 rows of this head, inside one page); otherwise the
+    // copy warp moves the 64 rows one by one, rows past the slot's last key replaced by that last key (always readable and
+    // finite, and masked in the softmax).
     auto issue = [&](int q) {
         const int s = q % nslot, it = q >> 1;
         unsigned char * dst = stg + (size_t) s * TR::SLOT;
         const char * base = (q & 1) ? a.g.v : a.g.k;
+        if constexpr (KT != B200_KV_F16) {
+            const int p_t = k_lo + it * TILE;
+            if (a.tiled && p_t + TILE <= n_slot) {
+                if (lane == 0) {
+                    int y = p_t, z = 0;
+                    if (tab) {
+                        z = tab[p_t >> a.g.psh];
+                        y = p_t & ((1 << a.g.psh) - 1);
+                        if (z < 0) { atomicOr(a.status, ST_BAD_PAGE); z = 0; }
+                    }
+                    mbar_expect_tx(&full[s], (uint32_t) TILE * HB);
+                    tma_box3(dst, (q & 1) ? &mapV : &mapK, hk * (HB / 2), y, z, &full[s]);
+                }
+                __syncwarp();
+                return;
+            }
+        }
         if (lane == 0) mbar_expect_tx(&full[s], (uint32_t) TILE * HB);
         __syncwarp();
 #pragma unroll
@@ -562,12 +593,53 @@ float * scratch_for(cudaStream_t s, size_t floats) {
     return e->p;
 }
 
+// ---- tensor maps of the cache ----------------------------------------------------------------------------------
+// K and V as rank-3 tensors of 16-bit elements: x = the row of one position (all kv heads), y = position inside a page
+// (or in the whole cache when it is contiguous), z = page.  The box is one head's bytes of 64 consecutive positions.
+using encode_tiled_fn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                     const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+encode_tiled_fn tensor_map_encoder() {
+    static encode_tiled_fn fn = [] {
+        void * p = nullptr;
+        cudaDriverEntryPointQueryResult r;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &r) != cudaSuccess || r != cudaDriverEntryPointSuccess) {
+            cudaGetLastError();
+            p = nullptr;
+        }
+        return (encode_tiled_fn) p;
+    }();
+    return fn;
+}
+bool make_cache_map(CUtensorMap * m, const char * base, const dec_args & a, int HB) {
+    encode_tiled_fn enc = tensor_map_encoder();
+    if (!enc) return false;
+    const bool paged = a.g.pt != nullptr;
+    const cuuint64_t rows = paged ? (cuuint64_t) 1 << a.g.psh : (cuuint64_t) a.n_ctx;
+    const cuuint64_t gdim[3] = {a.g.rowb / 2, rows, paged ? (cuuint64_t) 0x7fffffff : 1};
+    const cuuint64_t gstr[2] = {a.g.rowb, paged ? a.g.pstride : a.g.rowb * rows};
+    const cuuint32_t box[3] = {(cuuint32_t) HB / 2, (cuuint32_t) TILE, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    return enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, (void *) base, gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <uint32_t KT, int NT> size_t smem_bytes(int nslot) {
     return 128 + (size_t) nslot * traits<KT>::SLOT + NT * 8 * (QSTR + PSTR) + 8 * SDSTR + 2 * NWARP * NT * 8 * sizeof(float);
 }
 
 template <uint32_t KT, int NT>
-int launch_part(const dec_args & a, dim3 grid, cudaStream_t s) {
+int launch_part(const dec_args & a_in, dim3 grid, cudaStream_t s) {
+    dec_args a = a_in;
+    CUtensorMap mapK, mapV;
+    memset(&mapK, 0, sizeof mapK);
+    memset(&mapV, 0, sizeof mapV);
+    // tiled copies need a tile inside one page (pages of at least 64 rows), 16-byte row strides and a contiguous cache short
+    // enough for the stride field; anything else keeps the row-by-row copies
+    a.tiled = 0;
+    if (KT != B200_KV_F16 && (!a.g.pt || a.g.psh >= 6) && a.g.rowb % 16 == 0 &&
+        (a.g.pt ? a.g.pstride < ((unsigned long long) 1 << 40) : (a.n_ctx >= 1 && a.g.rowb * (unsigned long long) a.n_ctx < ((unsigned long long) 1 << 40))))
+        a.tiled = make_cache_map(&mapK, a.g.k, a, traits<KT>::HB) && make_cache_map(&mapV, a.g.v, a, traits<KT>::HB);
     // deepest ring (3..8 half-tile slots) that still lets three CTAs share an SM (227 KB usable); if three never fit, the
     // deepest that lets two
     auto fits = [](int n, int ctas) { return (size_t) ctas * (smem_bytes<KT, NT>(n) + 1024) <= (size_t) 227 * 1024; };
@@ -584,7 +656,7 @@ int launch_part(const dec_args & a, dim3 grid, cudaStream_t s) {
         cudaFuncSetAttribute(decode_part_k<KT, NT>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         attr_done[dev & 63] = true;
     }
-    decode_part_k<KT, NT><<<grid, NTHR_CTA, sm, s>>>(a, nslot);
+    decode_part_k<KT, NT><<<grid, NTHR_CTA, sm, s>>>(a, nslot, mapK, mapV);
     return B200_OK;
 }
 
@@ -639,6 +711,7 @@ int decode_impl(const float * q, const b200_kv_cache * c, float * out, const flo
     a.q_len = q_len; a.n_slots = n_slots; a.Hq = Hq;
     a.qscale = scale * LOG2E;
     a.CH = CH; a.max_chunks = max_chunks; a.status = st;
+    a.n_ctx = c->n_ctx; a.tiled = 0;
     const dim3 grid(max_chunks, c->Hkv, n_slots);
     int rc;
     if (c->type == B200_KV_F16) rc = launch_part_nt<B200_KV_F16>(a, grid, s);
@@ -714,6 +787,7 @@ int decode_noalloc_impl(const float * q, const b200_kv_cache * c, float * out, c
     a.q_len = q_len; a.n_slots = n_slots; a.Hq = Hq;
     a.qscale = scale * LOG2E;
     a.CH = CH; a.max_chunks = max_chunks; a.status = e->status;
+    a.n_ctx = c->n_ctx; a.tiled = 0;
     const dim3 grid(max_chunks, c->Hkv, n_slots);
     int rc;
     if (c->type == B200_KV_F16) rc = launch_part_nt<B200_KV_F16>(a, grid, s);
