@@ -1,8 +1,11 @@
 // Split-KV decode / MTP-verify attention over the paged f16 / q8_0 / q4_0 cache, sm_100a.
 //
-// Work unit = (slot, kv head, key chunk): one CTA of 4 warps walks its chunk in 64-key tiles.
-//   staging   K and V head rows of a tile are fetched by 1-D bulk async copies (TMA unit) into a multi-stage
-//             shared-memory ring, completion counted on mbarriers; rows keep their cache format in shared memory.
+// Work unit = (slot, kv head, key chunk): one CTA of 4 warps walks its chunk in 64-key tiles, four CTAs per SM.
+//   staging   the K rows and the V rows of a tile (one kv head, 64 positions) are each fetched by ONE tiled TMA copy through a
+//             tensor map of the cache (x = row bytes, y = position in page, z = page) into a ring of half-tile slots,
+//             completion counted on mbarriers; rows keep their cache format in shared memory.  The warp that is last to
+//             finish with a slot issues its refill.  Ragged last tiles, f16 caches and pages under 64 rows use per-row
+//             bulk copies instead.
 //   QK^T      warp w owns keys 16w..16w+15 of the tile: keys on the MMA M axis, the slot's 6 * q_len query rows on N
 //             (all GQA heads and verify rows share one pass over the KV bytes).  int8 / nibbles are widened to f16
 //             exactly in registers (byte permute + one f16x2 subtract), products accumulate in fp32 on the tensor
@@ -28,10 +31,13 @@ namespace b200 {
 namespace {
 
 constexpr int TILE = 64;              // keys per tile
-constexpr int NWARP = 4, NTHR = NWARP * 32;   // compute warps
-constexpr int NTHR_CTA = NTHR + 32;           // + one producer warp
-__device__ __forceinline__ void bar_tile() { asm volatile("bar.sync 1, %0;" ::"n"(NTHR_CTA) : "memory"); }   // compute + producer
-__device__ __forceinline__ void bar_compute() { asm volatile("bar.sync 2, %0;" ::"n"(NTHR) : "memory"); }   // compute warps only
+constexpr int NWARP = 4, NTHR = NWARP * 32;
+constexpr int PGS = 64;               // page-table entries of a chunk kept in shared memory
+constexpr int HDR = 128 + PGS * 4;    // shared-memory header: barriers, counters, page entries
+#ifndef DEC_CTAS
+#define DEC_CTAS 4
+#endif
+constexpr int CTAS_Q = DEC_CTAS;      // CTAs per SM the quantised kernels are compiled for (register budget 65536 / (128 * CTAS_Q))
 constexpr int QSTR = 576;             // bytes per Q row in shared memory (256 f16 + 64: rows g, g+1 on different bank halves)
 constexpr int PSTR = 144;             // bytes per P row (64 f16 + 16)
 constexpr int SDSTR = 132;            // bytes per V-scale row (64 f16 + 4)
@@ -99,7 +105,7 @@ template <int HI> __device__ __forceinline__ uint32_t cvt_n4x2(uint32_t u) {
 }
 
 template <uint32_t KT, int NT>
-__global__ void __launch_bounds__(NTHR_CTA, KT == B200_KV_F16 ? 2 : 3)
+__global__ void __launch_bounds__(NTHR, KT == B200_KV_F16 ? 2 : CTAS_Q)
 decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV) {
     using TR = traits<KT>;
     constexpr int HB = TR::HB, SROW = TR::SROW;
@@ -118,42 +124,32 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
 
     // shared memory carve-up
     uint64_t * full = reinterpret_cast<uint64_t *>(smem);                    // [nslot]
-    unsigned char * stg = smem + 128;                                        // nslot * SLOT
+    int * done = reinterpret_cast<int *>(smem + 96);                         // warps that finished Q K^T / P V (two counters)
+    int * pgs = reinterpret_cast<int *>(smem + 128);                         // [PGS] page-table entries of the chunk's pages
+    unsigned char * stg = smem + HDR;                                        // nslot * SLOT
     unsigned char * Qs = stg + (size_t) nslot * TR::SLOT;                    // [NT*8][QSTR]
     unsigned char * Ps = Qs + NT * 8 * QSTR;                                 // [NT*8][PSTR]
     unsigned char * Sd = Ps + NT * 8 * PSTR;                                 // [8][SDSTR]  V block scales, transposed
     float * wmax = reinterpret_cast<float *>(Sd + 8 * SDSTR);                // [NWARP][NT*8]
     float * wl = wmax + NWARP * NT * 8;                                      // [NWARP][NT*8]
 
-    if (tid == 0) {
-        for (int s = 0; s < nslot; ++s) mbar_init(&full[s], 1);
-        mbar_fence_init();
-    }
-    // Q rows -> shared memory as f16, scaled; row r = j * 6 + hh (verify row j, head hh of the group)
-    for (int i = tid; w < NWARP && i < NT * 8 * (DH / 4); i += NTHR) {
-        const int r = i / (DH / 4), d4 = (i - r * (DH / 4)) * 4;
-        float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        if (r < R) {
-            const int j = r / GQA, hh = r - j * GQA;
-            v = *reinterpret_cast<const float4 *>(a.q + ((size_t) (slot * a.q_len + j) * a.Hq + hk * GQA + hh) * DH + d4);
-        }
-        const float vv[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e)
-            *reinterpret_cast<__half *>(Qs + r * QSTR + q_slot<KT>(d4 + e) * 2) = __float2half_rn(vv[e] * a.qscale);
-    }
-    __syncthreads();
-
     const int32_t * tab = a.g.pt ? a.g.pt + (a.g.rtab ? a.g.rtab[slot * a.q_len] : 0) : nullptr;
     const unsigned long long hoff = (unsigned long long) hk * HB;
+    // the chunk's page-table entries are staged in shared memory when there are at most PGS of them, so that a refill does
+    // not wait for a global load
+    const int pg0 = tab ? k_lo >> a.g.psh : 0;
+    const bool pg_staged = tab && ((k_hi - 1) >> a.g.psh) - pg0 < PGS;
 
-    // producer: the K rows and the V rows of the tiles form one sequence q = 2 * tile (K), 2 * tile + 1 (V) that walks a ring
-    // of nslot half-tile slots, so a K slot is refilled as soon as its Q K^T is done.  A tile that lies inside the slot's
-    // keys is one tiled copy through the cache's tensor map (box = 64 rows of this head, inside one page); otherwise the
-    // copy warp moves the 64 rows one by one, rows past the slot's last key replaced by that last key (always readable and
-    // finite, and masked in the softmax).
-    auto issue = [&](int q) {
-        const int s = q % nslot, it = q >> 1;
+    // staging: the K rows and the V rows of the tiles form one sequence q = 2 * tile (K), 2 * tile + 1 (V) that walks a ring
+    // of nslot half-tile slots.  The warp that is last to finish the Q K^T (P V) of a tile refills that tile's K (V) slot with
+    // item q + nslot, so a copy is in flight while the other half of the tile is being computed.  A tile that lies inside
+    // the slot's keys is one tiled copy through the cache's tensor map (box = 64 rows of this head, inside one page);
+    // otherwise the warp moves the 64 rows one by one, rows past the slot's last key replaced by that last key (always
+    // readable and finite, and masked in the softmax).
+    auto page_of = [&](int p, bool first) { return pg_staged && !first ? pgs[(p >> a.g.psh) - pg0] : tab[p >> a.g.psh]; };
+    auto issue = [&](int q, int s, bool first) {   // s = q mod nslot; called by one whole warp
+        if (q >= 2 * ntiles) return;
+        const int it = q >> 1;
         unsigned char * dst = stg + (size_t) s * TR::SLOT;
         const char * base = (q & 1) ? a.g.v : a.g.k;
         if constexpr (KT != B200_KV_F16) {
@@ -162,7 +158,7 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
                 if (lane == 0) {
                     int y = p_t, z = 0;
                     if (tab) {
-                        z = tab[p_t >> a.g.psh];
+                        z = page_of(p_t, first);
                         y = p_t & ((1 << a.g.psh) - 1);
                         if (z < 0) { atomicOr(a.status, ST_BAD_PAGE); z = 0; }
                     }
@@ -181,24 +177,47 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
             const int p = min(k_lo + it * TILE + row, n_slot - 1);
             unsigned long long off;
             if (tab) {
-                const int pg = tab[p >> a.g.psh];
+                const int pg = page_of(p, first);
                 if (pg < 0) { atomicOr(a.status, ST_BAD_PAGE); off = 0; }
                 else off = (unsigned long long) pg * a.g.pstride + (unsigned long long) (p & ((1 << a.g.psh) - 1)) * a.g.rowb;
             } else off = (unsigned long long) p * a.g.rowb;
             bulk_g2s(dst + row * SROW, base + off + hoff, HB, &full[s]);
         }
     };
-    if (w == NWARP) {
-        // the producer warp fills the ring, then follows the compute warps tile by tile: when they pass the barrier of
-        // tile `it`, items up to 2 it (that tile's K, the previous tile's V) are consumed and their slots are refilled
-        int next_q = 0;
-        for (; next_q < nslot && next_q < 2 * ntiles; ++next_q) issue(next_q);
-        for (int it = 0; it < ntiles; ++it) {
-            bar_tile();
-            for (; next_q < 2 * ntiles && next_q <= 2 * it + nslot; ++next_q) issue(next_q);
+    // warp 0 starts the first copies before anything else, so that they fly while Q is staged
+    if (w == 0) {
+        if (lane == 0) {
+            for (int s = 0; s < nslot; ++s) mbar_init(&full[s], 1);
+            mbar_fence_init();
+            done[0] = done[1] = 0;
         }
-        return;
+        __syncwarp();
+        for (int q0 = 0; q0 < nslot; ++q0) issue(q0, q0, true);
     }
+    if (pg_staged)
+        for (int j = tid; j <= ((k_hi - 1) >> a.g.psh) - pg0; j += NTHR) pgs[j] = tab[pg0 + j];
+    // Q rows -> shared memory as f16, scaled; row r = j * 6 + hh (verify row j, head hh of the group)
+    for (int i = tid; i < NT * 8 * (DH / 4); i += NTHR) {
+        const int r = i / (DH / 4), d4 = (i - r * (DH / 4)) * 4;
+        float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (r < R) {
+            const int j = r / GQA, hh = r - j * GQA;
+            v = *reinterpret_cast<const float4 *>(a.q + ((size_t) (slot * a.q_len + j) * a.Hq + hk * GQA + hh) * DH + d4);
+        }
+        const float vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            *reinterpret_cast<__half *>(Qs + r * QSTR + q_slot<KT>(d4 + e) * 2) = __float2half_rn(vv[e] * a.qscale);
+    }
+    __syncthreads();
+
+    // consumed(c, q, s): this warp is done with item q in slot s; the last of the four warps refills the slot
+    auto consumed = [&](int c, int q, int s) {
+        asm volatile("" ::: "memory");   // the item's shared-memory reads stay above this point
+        int last = 0;
+        if (lane == 0) last = (atomicAdd(&done[c], 1) & (NWARP - 1)) == NWARP - 1;
+        if (__shfl_sync(0xffffffffu, last, 0)) issue(q + nslot, s, false);
+    };
 
     // per-lane row bookkeeping: this lane's score / output columns are rows 8i + 2t and 8i + 2t + 1
     int rpos[NT][2];
@@ -221,12 +240,22 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
             for (int e = 0; e < 4; ++e) O[mt][i][e] = 0.0f;
 
     const int kA = 16 * w + key_perm<KT>(g), kB = kA + 8;   // this lane's two keys (tile-relative) in the QK phase
+    int rmin = 0x7fffffff;   // the mask is only evaluated in tiles that reach past some row's last key or the chunk's end
+    for (int r = 0; r < R; ++r) rmin = min(rmin, row_pos(a, slot, r / GQA));
+    const int mask_from = min(k_hi, rmin + 1);
 
+    // ring position of the tile's K item (2 it) and V item (2 it + 1): slot index and the parity of its use count
+    int sk = 0, sv = 1 % nslot;
+    uint32_t phk = 0, phv = nslot == 1 ? 1u : 0u;
     for (int it = 0; it < ntiles; ++it) {
-        const int qk = 2 * it, qv = 2 * it + 1;
-        const unsigned char * Ks = stg + (size_t) (qk % nslot) * TR::SLOT;
-        const unsigned char * Vs = stg + (size_t) (qv % nslot) * TR::SLOT;
-        mbar_wait(&full[qk % nslot], (uint32_t) ((qk / nslot) & 1), a.status);
+        const unsigned char * Ks = stg + (size_t) sk * TR::SLOT;
+        const unsigned char * Vs = stg + (size_t) sv * TR::SLOT;
+        uint64_t * const bar_k = &full[sk], * const bar_v = &full[sv];
+        const uint32_t par_k = phk, par_v = phv;
+        const int sk_now = sk, sv_now = sv;
+        sk += 2; if (sk >= nslot) { sk -= nslot; phk ^= 1u; }
+        sv += 2; if (sv >= nslot) { sv -= nslot; phv ^= 1u; }
+        mbar_wait(bar_k, par_k, a.status);
 
         // ---------------- S = K Q^T for the warp's 16 keys ----------------
         float S[NT][4];
@@ -297,22 +326,30 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
                 }
             }
         }
+        consumed(0, 2 * it, sk_now);
         // causal / chunk mask, warp-level row maxima
         const int keyA = k_lo + it * TILE + kA, keyB = keyA + 8;
+        if (k_lo + (it + 1) * TILE > mask_from) {
+#pragma unroll
+            for (int i = 0; i < NT; ++i)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    if (keyA > rpos[i][e] || keyA >= k_hi) S[i][e] = B200_NEG_INF;
+                    if (keyB > rpos[i][e] || keyB >= k_hi) S[i][2 + e] = B200_NEG_INF;
+                }
+        }
 #pragma unroll
         for (int i = 0; i < NT; ++i)
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                if (keyA > rpos[i][e] || keyA >= k_hi) S[i][e] = B200_NEG_INF;
-                if (keyB > rpos[i][e] || keyB >= k_hi) S[i][2 + e] = B200_NEG_INF;
                 float mx = fmaxf(S[i][e], S[i][2 + e]);
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
                 if (g == 0) wmax[w * NT * 8 + 8 * i + 2 * t + e] = mx;
             }
-        bar_tile();   // B1: row maxima visible; every warp is done with the previous tile's PV (the producer refills slots)
-        mbar_wait(&full[qv % nslot], (uint32_t) ((qv / nslot) & 1), a.status);   // this tile's V rows
+        __syncthreads();   // B1: row maxima visible
+        mbar_wait(bar_v, par_v, a.status);   // this tile's V rows
 
         // ---------------- online softmax, P -> shared memory ----------------
         float fsc[NT][2];
@@ -328,8 +365,8 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
                 m_run[i][e] = mnew;
                 // P carries a factor 2^PSHIFT (numerator and denominator alike): keeps small weights out of the f16
                 // subnormal range
-                const __half pa = __float2half_rn(S[i][e] == B200_NEG_INF ? 0.0f : ex2f(S[i][e] - msafe + PSHIFT));
-                const __half pb = __float2half_rn(S[i][2 + e] == B200_NEG_INF ? 0.0f : ex2f(S[i][2 + e] - msafe + PSHIFT));
+                const __half pa = __float2half_rn(ex2f(S[i][e] - msafe + PSHIFT));       // 2^(-inf) = 0 for a masked key
+                const __half pb = __float2half_rn(ex2f(S[i][2 + e] - msafe + PSHIFT));
                 l_run[i][e] = fmaf(l_run[i][e], fsc[i][e], __half2float(pa) + __half2float(pb));
                 *reinterpret_cast<__half *>(Ps + r * PSTR + kA * 2) = pa;
                 *reinterpret_cast<__half *>(Ps + r * PSTR + kB * 2) = pb;
@@ -342,15 +379,20 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
                 *reinterpret_cast<uint16_t *>(Sd + b * SDSTR + key * 2) = *reinterpret_cast<const uint16_t *>(src);
             }
         }
-        // rescale the running output
+        // rescale the running output (the factors are exactly 1 while no row's maximum moves: skipped then)
+        bool moved = false;
 #pragma unroll
-        for (int mt = 0; mt < 4; ++mt)
+        for (int i = 0; i < NT; ++i) moved = moved || fsc[i][0] != 1.0f || fsc[i][1] != 1.0f;
+        if (__any_sync(0xffffffffu, moved)) {
 #pragma unroll
-            for (int i = 0; i < NT; ++i) {
-                O[mt][i][0] *= fsc[i][0]; O[mt][i][1] *= fsc[i][1];
-                O[mt][i][2] *= fsc[i][0]; O[mt][i][3] *= fsc[i][1];
-            }
-        bar_compute();   // B2: P and the V scales are visible
+            for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+                for (int i = 0; i < NT; ++i) {
+                    O[mt][i][0] *= fsc[i][0]; O[mt][i][1] *= fsc[i][1];
+                    O[mt][i][2] *= fsc[i][0]; O[mt][i][3] *= fsc[i][1];
+                }
+        }
+        __syncthreads();   // B2: P and the V scales are visible
 
         // ---------------- O^T += V^T P^T for the warp's 64 output dims ----------------
 #pragma unroll
@@ -420,6 +462,7 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
                 }
             }
         }
+        consumed(1, 2 * it + 1, sv_now);
     }
 
     // ---------------- write the unit's partial ----------------
@@ -434,7 +477,7 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
             l += __shfl_xor_sync(0xffffffffu, l, 16);
             if (g == 0) wl[w * NT * 8 + 8 * i + 2 * t + e] = l;
         }
-    bar_compute();
+    __syncthreads();
     const size_t unit = ((size_t) slot * a.g.Hkv + hk) * a.max_chunks + chunk;
     if (w == 0 && g == 0) {
 #pragma unroll
@@ -611,21 +654,47 @@ encode_tiled_fn tensor_map_encoder() {
     }();
     return fn;
 }
+// Encoding a map is pure host arithmetic on (base, geometry); the last few are kept, since a serving loop calls with the
+// same caches (one K and one V per layer) every step.
+struct map_entry { const char * base; unsigned long long rowb, pstride, rows; int HB; bool paged; CUtensorMap m; };
+constexpr int MAP_CACHE = 256;
+map_entry g_maps[MAP_CACHE];
+int g_nmaps = 0, g_map_next = 0;
+std::mutex g_map_mu;
+
 bool make_cache_map(CUtensorMap * m, const char * base, const dec_args & a, int HB) {
     encode_tiled_fn enc = tensor_map_encoder();
     if (!enc) return false;
     const bool paged = a.g.pt != nullptr;
     const cuuint64_t rows = paged ? (cuuint64_t) 1 << a.g.psh : (cuuint64_t) a.n_ctx;
+    const unsigned long long pstr = paged ? a.g.pstride : 0;
+    {
+        std::lock_guard<std::mutex> lk(g_map_mu);
+        for (int i = 0; i < g_nmaps; ++i) {
+            const map_entry & e = g_maps[i];
+            if (e.base == base && e.rowb == a.g.rowb && e.pstride == pstr && e.rows == rows && e.HB == HB && e.paged == paged) {
+                *m = e.m;
+                return true;
+            }
+        }
+    }
     const cuuint64_t gdim[3] = {a.g.rowb / 2, rows, paged ? (cuuint64_t) 0x7fffffff : 1};
     const cuuint64_t gstr[2] = {a.g.rowb, paged ? a.g.pstride : a.g.rowb * rows};
     const cuuint32_t box[3] = {(cuuint32_t) HB / 2, (cuuint32_t) TILE, 1};
     const cuuint32_t estr[3] = {1, 1, 1};
-    return enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, (void *) base, gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    if (enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, (void *) base, gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    std::lock_guard<std::mutex> lk(g_map_mu);
+    map_entry & e = g_maps[g_map_next];
+    g_map_next = (g_map_next + 1) % MAP_CACHE;
+    if (g_nmaps < MAP_CACHE) ++g_nmaps;
+    e.base = base; e.rowb = a.g.rowb; e.pstride = pstr; e.rows = rows; e.HB = HB; e.paged = paged; e.m = *m;
+    return true;
 }
 
 template <uint32_t KT, int NT> size_t smem_bytes(int nslot) {
-    return 128 + (size_t) nslot * traits<KT>::SLOT + NT * 8 * (QSTR + PSTR) + 8 * SDSTR + 2 * NWARP * NT * 8 * sizeof(float);
+    return HDR + (size_t) nslot * traits<KT>::SLOT + NT * 8 * (QSTR + PSTR) + 8 * SDSTR + 2 * NWARP * NT * 8 * sizeof(float);
 }
 
 template <uint32_t KT, int NT>
@@ -640,11 +709,12 @@ int launch_part(const dec_args & a_in, dim3 grid, cudaStream_t s) {
     if (KT != B200_KV_F16 && (!a.g.pt || a.g.psh >= 6) && a.g.rowb % 16 == 0 &&
         (a.g.pt ? a.g.pstride < ((unsigned long long) 1 << 40) : (a.n_ctx >= 1 && a.g.rowb * (unsigned long long) a.n_ctx < ((unsigned long long) 1 << 40))))
         a.tiled = make_cache_map(&mapK, a.g.k, a, traits<KT>::HB) && make_cache_map(&mapV, a.g.v, a, traits<KT>::HB);
-    // deepest ring (3..8 half-tile slots) that still lets three CTAs share an SM (227 KB usable); if three never fit, the
-    // deepest that lets two
+    // as many CTAs per SM as the kernel is compiled for, if a ring of two half-tile slots fits that often into the 227 KB of
+    // an SM; then the deepest ring (up to 8 slots) that still fits
     auto fits = [](int n, int ctas) { return (size_t) ctas * (smem_bytes<KT, NT>(n) + 1024) <= (size_t) 227 * 1024; };
-    int nslot = 3;
-    const int ctas = fits(3, 3) ? 3 : 2;
+    int ctas = KT == B200_KV_F16 ? 2 : CTAS_Q;
+    while (ctas > 1 && !fits(2, ctas)) --ctas;
+    int nslot = 2;
     while (nslot < 8 && fits(nslot + 1, ctas)) ++nslot;
     const size_t sm = smem_bytes<KT, NT>(nslot);
     static bool attr_done[64] = {};   // per instantiation and device
@@ -656,7 +726,7 @@ int launch_part(const dec_args & a_in, dim3 grid, cudaStream_t s) {
         cudaFuncSetAttribute(decode_part_k<KT, NT>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         attr_done[dev & 63] = true;
     }
-    decode_part_k<KT, NT><<<grid, NTHR_CTA, sm, s>>>(a, nslot, mapK, mapV);
+    decode_part_k<KT, NT><<<grid, NTHR, sm, s>>>(a, nslot, mapK, mapV);
     return B200_OK;
 }
 
