@@ -6,10 +6,11 @@
 //                (un-swizzled canonical layout, see umma.cuh), so the main kernel fetches a tile with one bulk copy.
 //   prefill_k    one CTA per (128 query rows of one kv head): rows n = 6 t + hh (token t, head hh of the GQA group) on
 //                the MMA M axis.  Per 64-key tile: S = Q K^T (tcgen05.mma, fp32 in tensor memory), online softmax in
-//                base 2 with one thread per row (no shuffles), P to shared memory as f16, O += P V accumulated in
-//                tensor memory.  Warp roles: 4 softmax warps, 1 bulk-copy producer warp, 1 MMA-issue warp; S of
-//                tile j+1 is computed (second S buffer in tensor memory) while the softmax of tile j runs.  The running output is rescaled only when a
-//                row's maximum grows by more than 2^8 (P stays below 256 in f16).  Epilogue: O / l, optional sigmoid gate.
+//                base 2 with one thread per row (no shuffles), P written as f16 over the S columns it came from (P V
+//                takes its A operand from tensor memory), O += P V accumulated in tensor memory.  Warp roles: 4 softmax
+//                warps, 1 bulk-copy producer warp, 1 MMA-issue warp; S of tile j+1 is computed (second S buffer in tensor
+//                memory) while the softmax of tile j runs.  The running output is rescaled only when a row's maximum
+//                grows by more than 2^8 (P stays below 256 in f16).  Epilogue: O / l, optional sigmoid gate.
 // f16 operands (int8 * f16 scale is not representable in bf16's 8 significand bits), fp32 accumulation.
 //
 // Reference counterparts: attn_fold (src/fast/attn_fold.cu:562-649: per chunk dequantise to f16 in scratch, HFMA2 tile
@@ -26,7 +27,7 @@ constexpr int BM = 128;                 // query rows per CTA
 constexpr int BN = 64;                  // keys per tile
 constexpr int IMG = BN * DH * 2;        // bytes of one tile image (32 KB)
 constexpr int Q_BYTES = BM * DH * 2;    // 64 KB
-constexpr int P_BYTES = BM * BN * 2;    // 16 KB
+constexpr int EPI_BYTES = 4 * 32 * 33 * 4;   // per softmax warp a 32 x 33 float tile for the row-wise epilogue
 constexpr int NTHR_PF = 192;            // 4 softmax warps + producer + MMA issuer
 constexpr float LOG2E_PF = 1.4426950408889634f;
 constexpr float RESCALE_GAP = 8.0f;     // rescale O when a row maximum grows by more than this (log2 units)
@@ -34,8 +35,8 @@ constexpr float RESCALE_GAP = 8.0f;     // rescale O when a row maximum grows by
 constexpr int NSTG = 3;                 // K and V ring depth (Q lives in tensor memory, not in shared memory)
 constexpr int SM_K = 0;                         // NSTG stages
 constexpr int SM_V = SM_K + NSTG * IMG;         // NSTG stages
-constexpr int SM_P = SM_V + NSTG * IMG;         // 2 buffers
-constexpr int SM_BAR = SM_P + 2 * P_BYTES;      // mbarriers + tmem base
+constexpr int SM_EPI = SM_V + NSTG * IMG;       // epilogue tiles
+constexpr int SM_BAR = SM_EPI + EPI_BYTES;      // mbarriers + tmem base
 constexpr int SM_TOTAL = SM_BAR + 256;
 
 // ---- pre-pass: cache rows -> f16 tile images -------------------------------------------------------------------
@@ -115,7 +116,7 @@ __global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
     extern __shared__ __align__(1024) unsigned char smem[];
     uint64_t * bars = reinterpret_cast<uint64_t *>(smem + SM_BAR);
     uint64_t * k_full = bars, * k_free = bars + 4, * v_full = bars + 8, * v_free = bars + 12, * s_full = bars + 16,
-             * s_free = bars + 18, * p_full = bars + 20, * p_free = bars + 22, * o_done = bars + 24, * q_ready = bars + 25;
+             * p_full = bars + 20, * pv_done = bars + 22, * o_done = bars + 24, * q_ready = bars + 25;
     uint32_t * tbase_p = reinterpret_cast<uint32_t *>(bars + 26);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -133,8 +134,8 @@ __global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
             mbar_init(&v_full[b], 1); mbar_init(&v_free[b], 1);
         }
         for (int b = 0; b < 2; ++b) {
-            mbar_init(&s_full[b], 1); mbar_init(&s_free[b], 128);
-            mbar_init(&p_full[b], 128); mbar_init(&p_free[b], 1);
+            mbar_init(&s_full[b], 1);
+            mbar_init(&p_full[b], 128); mbar_init(&pv_done[b], 1);
         }
         mbar_init(o_done, 1);
         mbar_init(q_ready, 1);
@@ -209,7 +210,8 @@ __global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
             auto issue_qk = [&](int j) {
                 const int b = j & 1, st = j % NSTG;
                 mbar_wait(&k_full[st], (uint32_t) ((j / NSTG) & 1), a.status);
-                if (j >= 2) mbar_wait(&s_free[b], (uint32_t) (((j >> 1) - 1) & 1), a.status);   // softmax of tile j-2 holds S in registers
+                // S buffer b still holds P of tile j-2 until P V of that tile has read it: that MMA was issued before this
+                // one by this thread, and the tensor pipe runs in issue order, so no barrier is needed
                 umma::fence_after_sync();
                 const uint32_t k_s = smem_u32(smem + SM_K + st * IMG);
 #pragma unroll 4
@@ -227,13 +229,14 @@ __global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
                 mbar_wait(&v_full[st], (uint32_t) ((j / NSTG) & 1), a.status);
                 mbar_wait(&p_full[b], (uint32_t) ((j >> 1) & 1), a.status);
                 umma::fence_after_sync();
-                const uint32_t p_s = smem_u32(smem + SM_P + b * P_BYTES), v_s = smem_u32(smem + SM_V + st * IMG);
+                const uint32_t v_s = smem_u32(smem + SM_V + st * IMG);
 #pragma unroll
-                for (int ks = 0; ks < BN / 16; ++ks)   // V image: MN-major, key groups of 8 contiguous (LBO 128), dim groups 1024 apart
-                    umma::mma_ss(t_O, umma::smem_desc(p_s + ks * 2 * 2048, 2048, 128), umma::smem_desc(v_s + ks * 2 * 128, 128, 1024),
+                for (int ks = 0; ks < BN / 16; ++ks)   // P from tensor memory (the first 32 columns of S buffer b: 16 keys = 8 columns
+                                                       // per step); V image: MN-major, key groups of 8 contiguous (LBO 128), dim groups 1024 apart
+                    umma::mma_ts(t_O, t_S + b * BN + ks * 8, umma::smem_desc(v_s + ks * 2 * 128, 128, 1024),
                                  id_pv, (j > 0 || ks > 0) ? 1u : 0u);
                 umma::commit(&v_free[st]);
-                umma::commit(&p_free[b]);
+                umma::commit(&pv_done[b]);
             }
             umma::commit(o_done);
         }
@@ -251,8 +254,6 @@ __global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
             umma::tmem_ld32(t_S + (j & 1) * BN + lane_off, sr[0]);
             umma::tmem_ld32(t_S + (j & 1) * BN + lane_off + 32, sr[1]);
             umma::tmem_ld_wait();
-            umma::fence_before_sync();
-            mbar_arrive(&s_free[j & 1]);
             const int k0 = j * BN;
             const bool diag = k0 + BN - 1 > pos;   // some key of the tile is masked for this row
             if (__any_sync(0xffffffffu, diag)) {
@@ -278,7 +279,7 @@ __global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
                     l *= f;
                 }
                 if (j > 0) {
-                    mbar_wait(&p_free[(j - 1) & 1], (uint32_t) (((j - 1) >> 1) & 1), a.status);   // P V of tile j-1 has landed in O
+                    mbar_wait(&pv_done[(j - 1) & 1], (uint32_t) (((j - 1) >> 1) & 1), a.status);   // P V of tile j-1 has landed in O
                     umma::fence_after_sync();
 #pragma unroll 1
                     for (int c0 = 0; c0 < DH; c0 += 32) {
@@ -293,27 +294,23 @@ __global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
                 }
             }
             const float mref_safe = m_ref == B200_NEG_INF ? 0.0f : m_ref;
-            if (j >= 2) mbar_wait(&p_free[j & 1], (uint32_t) (((j >> 1) - 1) & 1), a.status);   // P buffer no longer read
-            unsigned char * prow = smem + SM_P + (j & 1) * P_BYTES + r * 16;
+            // P (f16) overwrites the first 32 columns of this S buffer: column c of the row's lane = keys 2c, 2c+1, the A
+            // operand layout of P V.  S is in registers by now, and the next Q K^T into this buffer is queued behind P V.
+            uint32_t pw[32];
             float l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int h = 0; h < 2; ++h)
 #pragma unroll
-                for (int c8 = 0; c8 < 4; ++c8) {
-                    uint32_t w4[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        // ex2(-inf) = 0: masked keys need no special case (mref_safe is finite)
-                        const float p0 = ex2f(__uint_as_float(sr[h][c8 * 8 + 2 * e]) - mref_safe);
-                        const float p1 = ex2f(__uint_as_float(sr[h][c8 * 8 + 2 * e + 1]) - mref_safe);
-                        l4[e] += p0 + p1;
-                        w4[e] = pack_h2(p0, p1);
-                    }
-                    // key chunk kc = 4 h + c8 of the K-major P image: byte = kc * 2048 + row * 16
-                    *reinterpret_cast<uint4 *>(prow + (4 * h + c8) * 2048) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+                for (int c2 = 0; c2 < 16; ++c2) {
+                    // ex2(-inf) = 0: masked keys need no special case (mref_safe is finite)
+                    const float p0 = ex2f(__uint_as_float(sr[h][2 * c2]) - mref_safe);
+                    const float p1 = ex2f(__uint_as_float(sr[h][2 * c2 + 1]) - mref_safe);
+                    l4[c2 & 3] += p0 + p1;
+                    pw[16 * h + c2] = pack_h2(p0, p1);
                 }
             l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
-            umma::fence_async_smem();
+            umma::tmem_st32(t_S + (j & 1) * BN + lane_off, pw);
+            umma::tmem_st_wait();
             umma::fence_before_sync();
             mbar_arrive(&p_full[j & 1]);
         }
@@ -322,9 +319,9 @@ __global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
         umma::fence_after_sync();
         const float inv = l > 0.0f ? 1.0f / l : 0.0f;
         // Each warp owns the 32 rows of its tensor-memory lanes.  A 32-column slab of O goes through a private
-        // shared-memory tile (the P buffers are dead by now) so that global accesses run along rows: 8 lanes cover the 128
+        // shared-memory tile so that global accesses run along rows: 8 lanes cover the 128
         // bytes of one row, a warp instruction touches 4 rows.
-        float * tile = reinterpret_cast<float *>(smem + SM_P) + warp * (32 * 33);
+        float * tile = reinterpret_cast<float *>(smem + SM_EPI) + warp * (32 * 33);
         const int sub = lane >> 3, col = 4 * (lane & 7);
         size_t orow[8];
         bool live[8];
