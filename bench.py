@@ -38,6 +38,11 @@ N_ROT, ROPE_BASE, EPS = 64, 1e7, 1e-6
 KV_TYPES = {"f16": 1, "q4_0": 2, "q8_0": 8}
 HEAD_BYTES = {1: 512, 2: 144, 8: 272}
 
+# DRAM traffic figures taken from the ncu captures summarised under profiles/ (static: a profiler never runs inside a timed
+# bench).  Decode: traffic per algorithmic KV byte on the verify8 capture; it grows in proportion to the keys of a launch.
+DRAM_PER_ALGORITHMIC_BYTE = 397.8 / 362.5
+PREFILL8K_DRAM_BYTES = 657.7e6
+
 WORKLOADS = {
     # name: (slots, q_len, ctx_lo, ctx_hi, layers, default kv)
     "whole_box": (64, 4, 512, 65536, 16, "q8_0"),
@@ -421,8 +426,10 @@ def run_b200(args):
                          "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
                  "roofline": {"bound": "hbm", "kernel": "decode_part_k (+ merge) per layer call", "achieved": achieved,
                               "peak": peak, "peak_source": "measured" if peaks else "fallback", "unit": "GB/s",
-                              "frac": achieved / peak, "traffic": None, "avg_launch_ms": att_ms_avg,
-                              "algorithmic_bytes_per_launch": int(wl.kv_bytes_layer)}})
+                              "frac": achieved / peak, "traffic": int(DRAM_PER_ALGORITHMIC_BYTE * wl.kv_bytes_layer),
+                              "traffic_source": "dram read + write of one ncu capture of decode_part_k on verify8 (397.8 MB for 362.5 MB "
+                                                "of KV rows), scaled by the KV bytes of this launch",
+                              "avg_launch_ms": att_ms_avg, "algorithmic_bytes_per_launch": int(wl.kv_bytes_layer)}})
     if not args.no_cpu_baseline:
         smp = CpuSample(args, wl.n_ctx, wl.q_len, wl.kt)
         if smp.ok:
@@ -556,7 +563,9 @@ def run_prefill(args):
                         "d2h_bytes_per_step": int(h_o.numel() * 4)},
                 "roofline": {"bound": "tensor", "kernel": "kv_tiles_k + prefill_k", "achieved": ach, "peak": peak,
                              "peak_source": "measured burst" if peaks else "fallback", "unit": "TFLOP/s", "frac": ach / peak,
-                             "traffic": None, "avg_launch_ms": att_ms, "algorithmic_flops_per_launch": flops / nshard}}
+                             "traffic": int(PREFILL8K_DRAM_BYTES) if (T == 8192 and nshard == 1) else None,
+                             "traffic_source": "dram read + write of one ncu capture of prefill_k at T = 8192 (bytes)",
+                             "avg_launch_ms": att_ms, "algorithmic_flops_per_launch": flops / nshard}}
         if not args.no_cpu_baseline:
             line["cpu_baseline"] = {"value": None, "unit": "TFLOP/s", "cores": 0, "kind": "reference",
                                     "sample": "not timed for prefill: see the decode workloads for the CPU attention baseline"}

@@ -3,14 +3,17 @@
 // Two kernels per call:
 //   kv_tiles_k   dequantises the visible keys once into f16 "tile images" in scratch: per (kv head, 64-key tile) a
 //                32 KB K image and a 32 KB V image laid out exactly as the tensor core reads them from shared memory
-//                (un-swizzled canonical layout, see umma.cuh), so the main kernel fetches a tile with one bulk copy.
+//                (un-swizzled canonical layout, see umma.cuh; 8-key groups 4 KB apart, so two images side by side form
+//                one 128-key operand), so the main kernel fetches a tile with one bulk copy.
 //   prefill_k    one CTA per (128 query rows of one kv head): rows n = 6 t + hh (token t, head hh of the GQA group) on
-//                the MMA M axis.  Per 64-key tile: S = Q K^T (tcgen05.mma, fp32 in tensor memory), online softmax in
-//                base 2 with one thread per row (no shuffles), P written as f16 over the S columns it came from (P V
-//                takes its A operand from tensor memory), O += P V accumulated in tensor memory.  Warp roles: 4 softmax
-//                warps, 1 bulk-copy producer warp, 1 MMA-issue warp; S of tile j+1 is computed (second S buffer in tensor
-//                memory) while the softmax of tile j runs.  The running output is rescaled only when a row's maximum
-//                grows by more than 2^8 (P stays below 256 in f16).  Epilogue: O / l, optional sigmoid gate.
+//                the MMA M axis, keys in steps of 128 (a pair of images).  Per step: S = Q K^T as 16 MMAs m128n128k16
+//                (Q from tensor memory, fp32 S in tensor memory), online softmax in base 2 with two threads per row
+//                (64 keys each, no shuffles), P to shared memory as f16, O += P V as 8 MMAs m128n256k16 accumulated in
+//                tensor memory.  Warp roles: 8 softmax warps, 1 bulk-copy producer warp, 1 MMA-issue warp.  The MMA
+//                queue alternates Q K^T of step J+1 and P V of step J, so the tensor pipe has work while the softmax
+//                of a step runs; S is single-buffered (the next Q K^T starts when the softmax threads hold S in
+//                registers), P is double-buffered.  The running output is rescaled only when a row's maximum grows by
+//                more than 2^8 (P stays below 256 in f16).  Epilogue: O / l, optional sigmoid gate.
 // f16 operands (int8 * f16 scale is not representable in bf16's 8 significand bits), fp32 accumulation.
 //
 // Reference counterparts: attn_fold (src/fast/attn_fold.cu:562-649: per chunk dequantise to f16 in scratch, HFMA2 tile
@@ -24,24 +27,31 @@ namespace b200 {
 namespace {
 
 constexpr int BM = 128;                 // query rows per CTA
-constexpr int BN = 64;                  // keys per tile
+constexpr int BN = 64;                  // keys per tile image
+constexpr int BP = 2 * BN;              // keys per step: S tile = 128 rows x 128 keys
 constexpr int IMG = BN * DH * 2;        // bytes of one tile image (32 KB)
+constexpr int P_BYTES = BM * BP * 2;    // 32 KB
 constexpr int Q_BYTES = BM * DH * 2;    // 64 KB
-constexpr int EPI_BYTES = 4 * 32 * 33 * 4;   // per softmax warp a 32 x 33 float tile for the row-wise epilogue
-constexpr int NTHR_PF = 192;            // 4 softmax warps + producer + MMA issuer
+constexpr int EPI_BYTES = 8 * 32 * 33 * 4;   // per softmax warp a 32 x 33 float tile for the row-wise epilogue
+constexpr int NSOFT = 256;              // softmax threads: two per query row (key halves of a tile, dim halves of the output)
+constexpr int NTHR_PF = NSOFT + 64;     // 8 softmax warps + producer + MMA issuer
+constexpr int W_PROD = NSOFT / 32, W_MMA = W_PROD + 1;
 constexpr float LOG2E_PF = 1.4426950408889634f;
 constexpr float RESCALE_GAP = 8.0f;     // rescale O when a row maximum grows by more than this (log2 units)
 
-constexpr int NSTG = 3;                 // K and V ring depth (Q lives in tensor memory, not in shared memory)
-constexpr int SM_K = 0;                         // NSTG stages
-constexpr int SM_V = SM_K + NSTG * IMG;         // NSTG stages
-constexpr int SM_EPI = SM_V + NSTG * IMG;       // epilogue tiles
-constexpr int SM_BAR = SM_EPI + EPI_BYTES;      // mbarriers + tmem base
+constexpr int NSTG = 3;                         // V ring depth (64-key images)
+constexpr int SM_K = 0;                         // one pair of K images (the epilogue tiles reuse it)
+constexpr int SM_EPI = SM_K;
+constexpr int SM_V = SM_K + 2 * IMG;            // NSTG images
+constexpr int SM_P = SM_V + NSTG * IMG;         // 2 buffers
+constexpr int SM_XCH = SM_P + 2 * P_BYTES;      // [2][128] floats exchanged between the two threads of a row
+constexpr int SM_BAR = SM_XCH + 1024;           // mbarriers + tmem base
 constexpr int SM_TOTAL = SM_BAR + 256;
+static_assert(SM_TOTAL <= 227 * 1024 && EPI_BYTES <= 2 * IMG, "prefill_k shared memory");
 
 // ---- pre-pass: cache rows -> f16 tile images -------------------------------------------------------------------
-// grid (n_tiles, Hkv), 256 threads; thread = (key, 8-dim chunk).  Image byte of (key, dim) = (dim/8)*1024 + key*16 +
-// (dim%8)*2 for K (K-major B operand) and for V (MN-major B operand) alike.  Keys >= n_keys are zero.
+// grid (n_tiles, Hkv), 256 threads; thread = (key, 8-dim chunk).  Image byte of (key, dim) = (key/8)*4096 + (dim/8)*128 +
+// (key%8)*16 + (dim%8)*2 for K (K-major B operand) and for V (MN-major B operand) alike.  Keys >= n_keys are zero.
 template <uint32_t KT>
 __global__ void __launch_bounds__(256) kv_tiles_k(kv_view g, int n_keys, unsigned char * __restrict__ tiles, int n_tiles,
                                                   unsigned * status) {
@@ -89,8 +99,8 @@ __global__ void __launch_bounds__(256) kv_tiles_k(kv_view g, int n_keys, unsigne
                 }
             }
         }
-        *reinterpret_cast<uint4 *>(kimg + dc * 1024 + key * 16) = ko;
-        *reinterpret_cast<uint4 *>(vimg + dc * 1024 + key * 16) = vo;
+        *reinterpret_cast<uint4 *>(kimg + (key >> 3) * 4096 + dc * 128 + (key & 7) * 16) = ko;
+        *reinterpret_cast<uint4 *>(vimg + (key >> 3) * 4096 + dc * 128 + (key & 7) * 16) = vo;
     }
 }
 
@@ -115,9 +125,9 @@ __device__ __forceinline__ void mbar_arrive(uint64_t * bar) {
 __global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
     extern __shared__ __align__(1024) unsigned char smem[];
     uint64_t * bars = reinterpret_cast<uint64_t *>(smem + SM_BAR);
-    uint64_t * k_full = bars, * k_free = bars + 4, * v_full = bars + 8, * v_free = bars + 12, * s_full = bars + 16,
-             * p_full = bars + 20, * pv_done = bars + 22, * o_done = bars + 24, * q_ready = bars + 25;
-    uint32_t * tbase_p = reinterpret_cast<uint32_t *>(bars + 26);
+    uint64_t * k_full = bars, * k_free = bars + 1, * s_full = bars + 2, * s_free = bars + 3, * v_full = bars + 4, * v_free = bars + 8,
+             * p_full = bars + 12, * pv_done = bars + 14, * o_done = bars + 16, * q_ready = bars + 17;
+    uint32_t * tbase_p = reinterpret_cast<uint32_t *>(bars + 18);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int mtile = (int) gridDim.x - 1 - (int) blockIdx.x;   // heaviest (latest rows) first
@@ -126,17 +136,13 @@ __global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
     const int n0 = mtile * BM;
     const int t_last = min(n0 + BM - 1, R - 1) / GQA;           // last token of the tile
     const int n_keys_vis = a.p0 + t_last + 1;                   // keys any row of the tile can see
-    const int ntiles = (n_keys_vis + BN - 1) / BN;
+    const int ntiles = (n_keys_vis + BN - 1) / BN;              // 64-key images
+    const int nsteps = (ntiles + 1) / 2;                        // 128-key steps; the last one may hold a single image
 
     if (tid == 0) {
-        for (int b = 0; b < NSTG; ++b) {
-            mbar_init(&k_full[b], 1); mbar_init(&k_free[b], 1);
-            mbar_init(&v_full[b], 1); mbar_init(&v_free[b], 1);
-        }
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(&s_full[b], 1);
-            mbar_init(&p_full[b], 128); mbar_init(&pv_done[b], 1);
-        }
+        mbar_init(k_full, 1); mbar_init(k_free, 1); mbar_init(s_full, 1); mbar_init(s_free, NSOFT);
+        for (int b = 0; b < NSTG; ++b) { mbar_init(&v_full[b], 1); mbar_init(&v_free[b], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&p_full[b], NSOFT); mbar_init(&pv_done[b], 1); }
         mbar_init(o_done, 1);
         mbar_init(q_ready, 1);
         mbar_fence_init();
@@ -147,20 +153,20 @@ __global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
     __syncthreads();
     umma::fence_after_sync();
     const uint32_t tb = *tbase_p;
-    const uint32_t t_S = tb, t_O = tb + 2 * BN, t_Q = tb + 2 * BN + DH;   // S x2 at columns 0 / 64, O at 128..383, Q (f16 pairs) at 384..511
+    const uint32_t t_S = tb, t_O = tb + BP, t_Q = tb + BP + DH;   // S at columns 0..127, O at 128..383, Q (f16 pairs) at 384..511
 
-    if (warp < 4) {
-        // Q rows -> f16, scaled by softmax scale * log2(e), into tensor memory as the A operand of Q K^T: thread = row =
-        // lane, column c holds dims 2c, 2c+1.  64 dims per slab: 16 loads in flight per thread.
-        const int n = n0 + tid;
-        const uint32_t lane_off = (uint32_t) (warp * 32) << 16;
+    if (warp < W_PROD) {
+        // Q rows -> f16, scaled by softmax scale * log2(e), into tensor memory as the A operand of Q K^T: lane = row,
+        // column c holds dims 2c, 2c+1.  The two threads of a row take 128 dims each, 64 dims (16 loads in flight) per slab.
+        const int r = tid & (BM - 1), hf = tid >> 7, n = n0 + r;
+        const uint32_t lane_off = (uint32_t) ((warp & 3) * 32) << 16;
         const float4 * src = nullptr;
         if (n < R) {
             const int t = n / GQA, hh = n - t * GQA;
             src = reinterpret_cast<const float4 *>(a.q + ((size_t) t * a.Hq + hk * GQA + hh) * DH);
         }
 #pragma unroll 1
-        for (int d0 = 0; d0 < DH; d0 += 64) {
+        for (int d0 = hf * (DH / 2); d0 < (hf + 1) * (DH / 2); d0 += 64) {
             float4 x[16];
 #pragma unroll
             for (int u = 0; u < 16; ++u) x[u] = src ? __ldg(src + d0 / 4 + u) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
@@ -172,90 +178,107 @@ __global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
         }
         umma::tmem_st_wait();
         umma::fence_before_sync();
-        asm volatile("bar.sync 1, 128;" ::: "memory");   // the four softmax warps: every Q row is in place
+        asm volatile("bar.sync 1, %0;" ::"n"(NSOFT) : "memory");   // the softmax warps: every Q row is in place
         if (tid == 0) mbar_arrive(q_ready);
     }
-    if (warp >= 4 && a.gate && (lane & 15) != 0) {
+    if (warp >= W_PROD && a.gate && (lane & 15) != 0) {
         // idle lanes of the producer and MMA warps pull this CTA's gate rows (contiguous per token: 6 heads x 1 KB) into L2
         const int t_first = n0 / GQA;
         const char * g0 = reinterpret_cast<const char *>(a.gate + ((size_t) t_first * a.Hq + hk * GQA) * DH);
-        const int idx = (warp - 4) * 30 + lane - 1 - (lane > 16);
+        const int idx = (warp - W_PROD) * 30 + lane - 1 - (lane > 16);
         for (int t = t_first; t <= t_last; ++t)
             for (int ln = idx; ln < GQA * DH * 4 / 128; ln += 60)
                 asm volatile("prefetch.global.L2 [%0];" ::"l"(g0 + (size_t) (t - t_first) * a.Hq * DH * 4 + ln * 128));
     }
-    if (warp == 4) {
-        // ---------------- producer: one bulk copy per image; K (lane 0) and V (lane 16) rings run independently ----------------
+    if (warp == W_PROD) {
+        // ---------------- producer: K in pairs of images (lane 0), V image by image through a ring (lane 16) ----------------
         const unsigned char * src = a.tiles + (size_t) hk * a.n_tiles * (2 * IMG);
         if (lane == 0) {
-            for (int j = 0; j < ntiles; ++j) {
-                const int s = j % NSTG;
-                if (j >= NSTG) mbar_wait(&k_free[s], (uint32_t) ((j / NSTG - 1) & 1), a.status);   // Q K^T of tile j-NSTG has read the stage
-                mbar_expect_tx(&k_full[s], IMG);
-                bulk_g2s(smem + SM_K + s * IMG, src + (size_t) j * (2 * IMG), IMG, &k_full[s]);
+            for (int J = 0; J < nsteps; ++J) {
+                if (J >= 1) mbar_wait(k_free, (uint32_t) ((J - 1) & 1), a.status);   // Q K^T of step J-1 has read the pair
+                const int n_img = min(2, ntiles - 2 * J);
+                mbar_expect_tx(k_full, (uint32_t) n_img * IMG);
+                for (int h = 0; h < n_img; ++h)
+                    bulk_g2s(smem + SM_K + h * IMG, src + (size_t) (2 * J + h) * (2 * IMG), IMG, k_full);
             }
         } else if (lane == 16) {
             for (int j = 0; j < ntiles; ++j) {
                 const int s = j % NSTG;
-                if (j >= NSTG) mbar_wait(&v_free[s], (uint32_t) ((j / NSTG - 1) & 1), a.status);   // P V of tile j-NSTG has read the stage
+                if (j >= NSTG) mbar_wait(&v_free[s], (uint32_t) ((j / NSTG - 1) & 1), a.status);   // P V of image j-NSTG has read the slot
                 mbar_expect_tx(&v_full[s], IMG);
                 bulk_g2s(smem + SM_V + s * IMG, src + (size_t) j * (2 * IMG) + IMG, IMG, &v_full[s]);
             }
         }
-    } else if (warp == 5) {
-        // ---------------- MMA issuer: Q K^T of tile j+1 is queued before P V of tile j ----------------
+    } else if (warp == W_MMA) {
+        // ---------------- MMA issuer: Q K^T of step J+1 is queued before P V of step J ----------------
         if (lane == 0) {
-            constexpr uint32_t id_qk = umma::idesc_f16(BM, BN, false, false);   // S[128 x 64] = Q (K-major) * K^T (K-major)
+            constexpr uint32_t id_qk = umma::idesc_f16(BM, BP, false, false);   // S[128 x 128] = Q (tensor memory) * K^T (K-major)
             constexpr uint32_t id_pv = umma::idesc_f16(BM, DH, false, true);    // O[128 x 256] += P (K-major) * V (MN-major)
-            auto issue_qk = [&](int j) {
-                const int b = j & 1, st = j % NSTG;
-                mbar_wait(&k_full[st], (uint32_t) ((j / NSTG) & 1), a.status);
-                // S buffer b still holds P of tile j-2 until P V of that tile has read it: that MMA was issued before this
-                // one by this thread, and the tensor pipe runs in issue order, so no barrier is needed
+            const uint32_t k_s = smem_u32(smem + SM_K);
+            auto issue_qk = [&](int J) {
+                mbar_wait(k_full, (uint32_t) (J & 1), a.status);
+                if (J >= 1) mbar_wait(s_free, (uint32_t) ((J - 1) & 1), a.status);   // the softmax threads hold S of step J-1 in registers
                 umma::fence_after_sync();
-                const uint32_t k_s = smem_u32(smem + SM_K + st * IMG);
+                // K pair: K-major, 8-key groups 4096 apart (SBO), 8-dim chunks 128 apart (LBO); 16 dims = 256 bytes per k-step.
+                // A step with a single image multiplies whatever the second half of the buffer holds: those keys lie past
+                // every row of the tile and are masked.
 #pragma unroll 4
                 for (int ks = 0; ks < DH / 16; ++ks)
-                    umma::mma_ts(t_S + b * BN, t_Q + ks * 8, umma::smem_desc(k_s + ks * 2 * 1024, 1024, 128), id_qk, ks > 0);   // Q from tensor memory
-                umma::commit(&s_full[b]);
-                umma::commit(&k_free[st]);
+                    umma::mma_ts(t_S, t_Q + ks * 8, umma::smem_desc(k_s + ks * 256, 128, 4096), id_qk, ks > 0);
+                umma::commit(s_full);
+                umma::commit(k_free);
+            };
+            auto issue_pv = [&](int J) {
+                const int b = J & 1;
+                mbar_wait(&p_full[b], (uint32_t) ((J >> 1) & 1), a.status);
+                const uint32_t p_s = smem_u32(smem + SM_P + b * P_BYTES);
+                const int n_img = min(2, ntiles - 2 * J);
+                for (int h = 0; h < n_img; ++h) {
+                    const int j = 2 * J + h, st = j % NSTG;
+                    mbar_wait(&v_full[st], (uint32_t) ((j / NSTG) & 1), a.status);
+                    umma::fence_after_sync();
+                    const uint32_t v_s = smem_u32(smem + SM_V + st * IMG);
+#pragma unroll
+                    for (int ks = 0; ks < BN / 16; ++ks)   // P: K-major, 8-key chunks 2048 apart; V: MN-major, 8-key groups 4096 apart (LBO),
+                                                           // 8-dim chunks 128 apart (SBO)
+                        umma::mma_ss(t_O, umma::smem_desc(p_s + (h * 4 + ks) * 2 * 2048, 2048, 128),
+                                     umma::smem_desc(v_s + ks * 2 * 4096, 4096, 128), id_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                    umma::commit(&v_free[st]);
+                }
+                umma::commit(&pv_done[b]);
             };
             mbar_wait(q_ready, 0, a.status);
             umma::fence_after_sync();
             issue_qk(0);
-            for (int j = 0; j < ntiles; ++j) {
-                if (j + 1 < ntiles) issue_qk(j + 1);
-                const int b = j & 1, st = j % NSTG;
-                mbar_wait(&v_full[st], (uint32_t) ((j / NSTG) & 1), a.status);
-                mbar_wait(&p_full[b], (uint32_t) ((j >> 1) & 1), a.status);
-                umma::fence_after_sync();
-                const uint32_t v_s = smem_u32(smem + SM_V + st * IMG);
-#pragma unroll
-                for (int ks = 0; ks < BN / 16; ++ks)   // P from tensor memory (the first 32 columns of S buffer b: 16 keys = 8 columns
-                                                       // per step); V image: MN-major, key groups of 8 contiguous (LBO 128), dim groups 1024 apart
-                    umma::mma_ts(t_O, t_S + b * BN + ks * 8, umma::smem_desc(v_s + ks * 2 * 128, 128, 1024),
-                                 id_pv, (j > 0 || ks > 0) ? 1u : 0u);
-                umma::commit(&v_free[st]);
-                umma::commit(&pv_done[b]);
+            for (int J = 0; J < nsteps; ++J) {
+                if (J + 1 < nsteps) issue_qk(J + 1);
+                issue_pv(J);
             }
             umma::commit(o_done);
         }
     } else {
-        // ---------------- softmax: thread = row ----------------
-        const int r = tid, n = n0 + r;
+        // ---------------- softmax: two threads per row ----------------
+        // Thread (row r, half hf) owns keys 64 hf .. 64 hf + 63 of every step and, in the epilogue, output dims 128 hf ..
+        // The two warps that share 32 rows (warps w and w + 4, the same tensor-memory lanes) meet once per step at a
+        // 64-thread barrier that ORs their "a maximum grew" votes; both keep the same reference maximum in registers.
+        const int r = tid & (BM - 1), hf = tid >> 7, n = n0 + r;
         const int t_row = n / GQA;
         const int pos = n < R ? a.p0 + t_row : -1;
-        const uint32_t lane_off = (uint32_t) (warp * 32) << 16;
+        const int pair_bar = 2 + (warp & 3);
+        const uint32_t lane_off = (uint32_t) ((warp & 3) * 32) << 16;
+        float * xch = reinterpret_cast<float *>(smem + SM_XCH);
         float m_ref = B200_NEG_INF, l = 0.0f;
-        for (int j = 0; j < ntiles; ++j) {
-            mbar_wait(&s_full[j & 1], (uint32_t) ((j >> 1) & 1), a.status);
+        for (int J = 0; J < nsteps; ++J) {
+            mbar_wait(s_full, (uint32_t) (J & 1), a.status);
             umma::fence_after_sync();
             uint32_t sr[2][32];
-            umma::tmem_ld32(t_S + (j & 1) * BN + lane_off, sr[0]);
-            umma::tmem_ld32(t_S + (j & 1) * BN + lane_off + 32, sr[1]);
+            umma::tmem_ld32(t_S + lane_off + 64 * hf, sr[0]);
+            umma::tmem_ld32(t_S + lane_off + 64 * hf + 32, sr[1]);
             umma::tmem_ld_wait();
-            const int k0 = j * BN;
-            const bool diag = k0 + BN - 1 > pos;   // some key of the tile is masked for this row
+            umma::fence_before_sync();
+            mbar_arrive(s_free);   // S is in registers: the next Q K^T may overwrite it
+            const int k0 = J * BP + 64 * hf;
+            const bool diag = k0 + 63 > pos;   // some key of this half is masked for this row
             if (__any_sync(0xffffffffu, diag)) {
 #pragma unroll
                 for (int h = 0; h < 2; ++h)
@@ -269,20 +292,27 @@ __global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
 #pragma unroll
                 for (int c = 0; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[h][c]));
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            // lazy rescale: only when some row of the warp outgrew its reference maximum
-            const bool grow = mx > m_ref + RESCALE_GAP || (m_ref == B200_NEG_INF && mx != B200_NEG_INF);
-            if (__any_sync(0xffffffffu, grow)) {
+            // lazy rescale: only when some row of the warp pair outgrew its reference maximum
+            const int grow_here = mx > m_ref + RESCALE_GAP || (m_ref == B200_NEG_INF && mx != B200_NEG_INF);
+            int grow_any;
+            asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.s32 q, %1, 0;\n\tbarrier.red.or.pred p, %2, 64, q;\n\tselp.s32 %0, 1, 0, p;\n\t}"
+                         : "=r"(grow_any) : "r"(grow_here), "r"(pair_bar) : "memory");
+            if (grow_any) {
+                xch[hf * BM + r] = mx;
+                asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+                const float mxr = fmaxf(xch[r], xch[BM + r]);
+                asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");   // both have read before the next use of xch
                 float f = 1.0f;
-                if (grow) {
-                    f = m_ref == B200_NEG_INF ? 0.0f : ex2f(m_ref - mx);
-                    m_ref = mx;
+                if (mxr > m_ref + RESCALE_GAP || (m_ref == B200_NEG_INF && mxr != B200_NEG_INF)) {
+                    f = m_ref == B200_NEG_INF ? 0.0f : ex2f(m_ref - mxr);
+                    m_ref = mxr;
                     l *= f;
                 }
-                if (j > 0) {
-                    mbar_wait(&pv_done[(j - 1) & 1], (uint32_t) (((j - 1) >> 1) & 1), a.status);   // P V of tile j-1 has landed in O
+                if (J > 0) {
+                    mbar_wait(&pv_done[(J - 1) & 1], (uint32_t) (((J - 1) >> 1) & 1), a.status);   // P V of step J-1 has landed in O
                     umma::fence_after_sync();
 #pragma unroll 1
-                    for (int c0 = 0; c0 < DH; c0 += 32) {
+                    for (int c0 = hf * (DH / 2); c0 < (hf + 1) * (DH / 2); c0 += 32) {
                         uint32_t o[32];
                         umma::tmem_ld32(t_O + lane_off + c0, o);
                         umma::tmem_ld_wait();
@@ -291,43 +321,52 @@ __global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
                         umma::tmem_st32(t_O + lane_off + c0, o);
                     }
                     umma::tmem_st_wait();
+                    umma::fence_before_sync();
                 }
             }
             const float mref_safe = m_ref == B200_NEG_INF ? 0.0f : m_ref;
-            // P (f16) overwrites the first 32 columns of this S buffer: column c of the row's lane = keys 2c, 2c+1, the A
-            // operand layout of P V.  S is in registers by now, and the next Q K^T into this buffer is queued behind P V.
-            uint32_t pw[32];
+            if (J >= 2) mbar_wait(&pv_done[J & 1], (uint32_t) (((J >> 1) - 1) & 1), a.status);   // P buffer no longer read
+            // K-major P image of the step: key chunk kc (8 keys) at kc * 2048, row at 16 bytes; this thread's chunks are 8 hf ..
+            unsigned char * prow = smem + SM_P + (J & 1) * P_BYTES + (8 * hf) * 2048 + r * 16;
             float l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int h = 0; h < 2; ++h)
 #pragma unroll
-                for (int c2 = 0; c2 < 16; ++c2) {
-                    // ex2(-inf) = 0: masked keys need no special case (mref_safe is finite)
-                    const float p0 = ex2f(__uint_as_float(sr[h][2 * c2]) - mref_safe);
-                    const float p1 = ex2f(__uint_as_float(sr[h][2 * c2 + 1]) - mref_safe);
-                    l4[c2 & 3] += p0 + p1;
-                    pw[16 * h + c2] = pack_h2(p0, p1);
+                for (int c8 = 0; c8 < 4; ++c8) {
+                    uint32_t w4[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        // ex2(-inf) = 0: masked keys need no special case (mref_safe is finite)
+                        const float p0 = ex2f(__uint_as_float(sr[h][c8 * 8 + 2 * e]) - mref_safe);
+                        const float p1 = ex2f(__uint_as_float(sr[h][c8 * 8 + 2 * e + 1]) - mref_safe);
+                        l4[e] += p0 + p1;
+                        w4[e] = pack_h2(p0, p1);
+                    }
+                    *reinterpret_cast<uint4 *>(prow + (4 * h + c8) * 2048) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
                 }
             l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
-            umma::tmem_st32(t_S + (j & 1) * BN + lane_off, pw);
-            umma::tmem_st_wait();
+            umma::fence_async_smem();
             umma::fence_before_sync();
-            mbar_arrive(&p_full[j & 1]);
+            mbar_arrive(&p_full[J & 1]);
         }
         // ---------------- epilogue: O / l, gate, store ----------------
+        xch[hf * BM + r] = l;
+        asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+        l = xch[r] + xch[BM + r];
         mbar_wait(o_done, 0, a.status);
         umma::fence_after_sync();
         const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-        // Each warp owns the 32 rows of its tensor-memory lanes.  A 32-column slab of O goes through a private
-        // shared-memory tile so that global accesses run along rows: 8 lanes cover the 128
-        // bytes of one row, a warp instruction touches 4 rows.
+        // Each warp owns the 32 rows of its tensor-memory lanes and the dim half of its threads.  A 32-column slab of O goes
+        // through a private shared-memory tile so that global accesses run along rows: 8 lanes cover the 128 bytes of one
+        // row, a warp instruction touches 4 rows.
         float * tile = reinterpret_cast<float *>(smem + SM_EPI) + warp * (32 * 33);
         const int sub = lane >> 3, col = 4 * (lane & 7);
+        const int c_lo = hf * (DH / 2), c_hi = c_lo + DH / 2;
         size_t orow[8];
         bool live[8];
 #pragma unroll
         for (int q8 = 0; q8 < 8; ++q8) {
-            const int nr = n0 + warp * 32 + 4 * q8 + sub;
+            const int nr = n0 + (warp & 3) * 32 + 4 * q8 + sub;
             const int tr = nr / GQA, hr = nr - tr * GQA;
             live[q8] = nr < R;
             orow[q8] = ((size_t) tr * a.Hq + hk * GQA + hr) * DH + col;
@@ -335,14 +374,14 @@ __global__ void __launch_bounds__(NTHR_PF, 1) prefill_k(const pf_args a) {
         float4 gn[8];   // gate values of the next slab, requested one slab ahead
 #pragma unroll
         for (int q8 = 0; q8 < 8; ++q8)
-            gn[q8] = (a.gate && live[q8]) ? __ldg(reinterpret_cast<const float4 *>(a.gate + orow[q8])) : make_float4(0.f, 0.f, 0.f, 0.f);
+            gn[q8] = (a.gate && live[q8]) ? __ldg(reinterpret_cast<const float4 *>(a.gate + orow[q8] + c_lo)) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 1
-        for (int c0 = 0; c0 < DH; c0 += 32) {
+        for (int c0 = c_lo; c0 < c_hi; c0 += 32) {
             float4 gv[8];
 #pragma unroll
             for (int q8 = 0; q8 < 8; ++q8) {
                 gv[q8] = gn[q8];
-                if (a.gate && live[q8] && c0 + 32 < DH) gn[q8] = __ldg(reinterpret_cast<const float4 *>(a.gate + orow[q8] + c0 + 32));
+                if (a.gate && live[q8] && c0 + 32 < c_hi) gn[q8] = __ldg(reinterpret_cast<const float4 *>(a.gate + orow[q8] + c0 + 32));
             }
             uint32_t o[32];
             umma::tmem_ld32(t_O + lane_off + c0, o);
