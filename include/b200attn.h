@@ -159,6 +159,14 @@ int b200_attn_decode_slots_partial(const float *q, const b200_kv_cache *c, float
  * part_o [nparts][R][D], part_m / part_l [nparts][R], gate / out [R][D]. */
 int b200_attn_merge_gate(const float *part_o, const float *part_m, const float *part_l, int nparts, int R, int D,
                          const float *gate, float *out, void *stream);
+/* The exchange + merge step of the sequence split for a host that drives NCCL itself (the reference links NCCL for its
+ * tensor-parallel all-reduce, src/tp_model.cu:41 `#include <nccl.h>`; it has no sequence split, so this entry has no
+ * reference twin).  send = this shard's partial as one flat buffer [O (R*D) | m (R) | l (R)] (the three outputs of
+ * b200_attn_decode_slots_partial placed back to back), recv = n_seq such buffers.  ncclAllGather over `nccl_comm`
+ * (an ncclComm_t of the n_seq shards, rank order = shard order) on `stream`, then the merge of b200_attn_merge_gate.
+ * n_seq == 1 merges `send` alone.  NCCL is not linked: the symbol is taken from the NCCL library already loaded. */
+int b200_seq_exchange_merge(void *nccl_comm, int n_seq, const float *send, float *recv, int R, int D, const float *gate,
+                            float *out, void *stream);
 int b200_attn_chunk_keys(void); /* the default chunk (keys) used by the reference-compatible entry points */
 
 /* ---------------------------------------------------------------- prefill ------------------------------------ */

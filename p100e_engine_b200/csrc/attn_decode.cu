@@ -21,6 +21,7 @@
 // Reference counterpart: dec2_k / attn_decode2 (src/fast/attn_dec2.cu:210-530), fp32 FFMA on sm_60.
 #include "common.cuh"
 
+#include <dlfcn.h>
 #include <cuda.h>   // CUtensorMap and its enums only: the encoder is looked up at run time, nothing links against libcuda
 #include <algorithm>
 #include <cstring>
@@ -33,7 +34,7 @@ namespace {
 constexpr int TILE = 64;              // keys per tile
 constexpr int NWARP = 4, NTHR = NWARP * 32;
 constexpr int PGS = 64;               // page-table entries of a chunk kept in shared memory
-constexpr int HDR = 128 + PGS * 4;    // shared-memory header: barriers, counters, page entries
+constexpr int HDR = 1024;             // shared-memory header: barriers, counters, page entries; the slots start 1024-aligned
 #ifndef DEC_CTAS
 #define DEC_CTAS 4
 #endif
@@ -47,10 +48,16 @@ constexpr float PSHIFT = 8.0f;        // P (and l) are kept times 2^8 inside the
 
 template <uint32_t KT> struct traits {
     static constexpr int HB = head_bytes(KT);                       // bytes of a head row in the cache
-    static constexpr int SROW = KT == B200_KV_F16 ? HB + 16 : HB;   // bytes per key row in shared memory (= 4 mod 32 words)
+    static constexpr int SROW = HB;                                 // bytes per key row in shared memory
     static constexpr int SLOT = TILE * SROW;                        // one ring slot: the K rows or the V rows of a tile
     static constexpr bool SCALED = KT != B200_KV_F16;
 };
+// f16 slots hold four sub-tiles [64 rows][128 B] (dims 64 c .. 64 c + 63) with the 128-byte swizzle of the TMA unit: the
+// 16-byte chunk j of a sub-tile row sits at chunk j ^ (row & 7), which keeps 16-byte and ldmatrix accesses of eight
+// different rows on different banks.  chunk16 = 16-byte chunk of the 512-byte head row.
+__device__ __forceinline__ int f16_slot_off(int row, int chunk16) {
+    return (chunk16 >> 3) * (TILE * 128) + row * 128 + (((chunk16 & 7) ^ (row & 7)) << 4);
+}
 
 // M-row (0..7) -> key of the warp's 16-key group, chosen so that the A-fragment loads of a phase hit distinct banks
 template <uint32_t KT> __device__ __forceinline__ int key_perm(int g) {
@@ -104,12 +111,17 @@ template <int HI> __device__ __forceinline__ uint32_t cvt_n4x2(uint32_t u) {
     return hsub2_u32(__byte_perm(u, 0x64646464u, HI ? 0x7362 : 0x5140), 0x64086408u);
 }
 
+__device__ __forceinline__ void tma_box4(void * dst, const CUtensorMap * map, int x, int y, int z, int w, uint64_t * bar) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(w), "r"(smem_u32(bar)) : "memory");
+}
+
 template <uint32_t KT, int NT>
 __global__ void __launch_bounds__(NTHR, KT == B200_KV_F16 ? 2 : CTAS_Q)
 decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV) {
     using TR = traits<KT>;
     constexpr int HB = TR::HB, SROW = TR::SROW;
-    extern __shared__ __align__(128) unsigned char smem[];
+    extern __shared__ __align__(1024) unsigned char smem[];
     const int chunk = blockIdx.x, hk = blockIdx.y, slot = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, g = lane >> 2, t = lane & 3;
     const int R = a.q_len * GQA;
@@ -152,37 +164,40 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
         const int it = q >> 1;
         unsigned char * dst = stg + (size_t) s * TR::SLOT;
         const char * base = (q & 1) ? a.g.v : a.g.k;
-        if constexpr (KT != B200_KV_F16) {
-            const int p_t = k_lo + it * TILE;
-            if (a.tiled && p_t + TILE <= n_slot) {
-                if (lane == 0) {
-                    int y = p_t, z = 0;
-                    if (tab) {
-                        z = page_of(p_t, first);
-                        y = p_t & ((1 << a.g.psh) - 1);
-                        if (z < 0) { atomicOr(a.status, ST_BAD_PAGE); z = 0; }
-                    }
-                    mbar_expect_tx(&full[s], (uint32_t) TILE * HB);
-                    tma_box3(dst, (q & 1) ? &mapV : &mapK, hk * (HB / 2), y, z, &full[s]);
+        const int p_t = k_lo + it * TILE;
+        if (a.tiled && p_t + TILE <= n_slot) {
+            if (lane == 0) {
+                int y = p_t, z = 0;
+                if (tab) {
+                    z = page_of(p_t, first);
+                    y = p_t & ((1 << a.g.psh) - 1);
+                    if (z < 0) { atomicOr(a.status, ST_BAD_PAGE); z = 0; }
                 }
-                __syncwarp();
-                return;
+                mbar_expect_tx(&full[s], (uint32_t) TILE * HB);
+                if constexpr (KT == B200_KV_F16) tma_box4(dst, (q & 1) ? &mapV : &mapK, 0, y, 4 * hk, z, &full[s]);
+                else tma_box3(dst, (q & 1) ? &mapV : &mapK, hk * (HB / 2), y, z, &full[s]);
             }
+            __syncwarp();
+            return;
         }
-        if (lane == 0) mbar_expect_tx(&full[s], (uint32_t) TILE * HB);
-        __syncwarp();
-#pragma unroll
-        for (int rr = 0; rr < TILE / 32; ++rr) {
-            const int row = lane + 32 * rr;
-            const int p = min(k_lo + it * TILE + row, n_slot - 1);
+        // row by row through registers, 16 bytes per lane and step; the slot is published by a plain arrival
+        constexpr int CPR = HB / 16;
+#pragma unroll 4
+        for (int idx = lane; idx < TILE * CPR; idx += 32) {
+            const int row = idx / CPR, c = idx - row * CPR;
+            const int p = min(p_t + row, n_slot - 1);
             unsigned long long off;
             if (tab) {
                 const int pg = page_of(p, first);
                 if (pg < 0) { atomicOr(a.status, ST_BAD_PAGE); off = 0; }
                 else off = (unsigned long long) pg * a.g.pstride + (unsigned long long) (p & ((1 << a.g.psh) - 1)) * a.g.rowb;
             } else off = (unsigned long long) p * a.g.rowb;
-            bulk_g2s(dst + row * SROW, base + off + hoff, HB, &full[s]);
+            const uint4 v = __ldg(reinterpret_cast<const uint4 *>(base + off + hoff) + c);
+            const int o = KT == B200_KV_F16 ? f16_slot_off(row, c) : row * SROW + c * 16;
+            *reinterpret_cast<uint4 *>(dst + o) = v;
         }
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&full[s])) : "memory");
     };
     // warp 0 starts the first copies before anything else, so that they fly while Q is staged
     if (w == 0) {
@@ -241,7 +256,7 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
 
     const int kA = 16 * w + key_perm<KT>(g), kB = kA + 8;   // this lane's two keys (tile-relative) in the QK phase
     int rmin = 0x7fffffff;   // the mask is only evaluated in tiles that reach past some row's last key or the chunk's end
-    for (int r = 0; r < R; ++r) rmin = min(rmin, row_pos(a, slot, r / GQA));
+    for (int j = 0; j < a.q_len; ++j) rmin = min(rmin, row_pos(a, slot, j));
     const int mask_from = min(k_hi, rmin + 1);
 
     // ring position of the tile's K item (2 it) and V item (2 it + 1): slot index and the parity of its use count
@@ -265,8 +280,8 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
         if constexpr (KT == B200_KV_F16) {
 #pragma unroll
             for (int b = 0; b < NBLK; ++b) {
-                const uint4 wa = *reinterpret_cast<const uint4 *>(rowA + 64 * b + 16 * t);
-                const uint4 wb = *reinterpret_cast<const uint4 *>(rowB + 64 * b + 16 * t);
+                const uint4 wa = *reinterpret_cast<const uint4 *>(Ks + f16_slot_off(kA, 4 * b + t));
+                const uint4 wb = *reinterpret_cast<const uint4 *>(Ks + f16_slot_off(kB, 4 * b + t));
                 const uint32_t a0[4] = {wa.x, wb.x, wa.y, wb.y}, a1[4] = {wa.z, wb.z, wa.w, wb.w};
 #pragma unroll
                 for (int i = 0; i < NT; ++i) {
@@ -408,7 +423,7 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
                 for (int mt = 0; mt < 4; ++mt) {
                     // four 8x8 tiles, transposed on load: (keys 0-7 | 8-15) x (dims 0-7 | 8-15) of this m-tile
                     const int mj = lane >> 3, mr = lane & 7;
-                    const unsigned char * p = Vs + (16 * u + (mj >> 1) * 8 + mr) * SROW + (64 * w + 16 * mt + (mj & 1) * 8) * 2;
+                    const unsigned char * p = Vs + f16_slot_off(16 * u + (mj >> 1) * 8 + mr, 8 * w + 2 * mt + (mj & 1));
                     uint32_t av[4];
                     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                                  : "=r"(av[0]), "=r"(av[1]), "=r"(av[2]), "=r"(av[3]) : "r"(smem_u32(p)));
@@ -563,21 +578,22 @@ __global__ void __launch_bounds__(64) decode_merge_k(const dec_args a, const flo
     }
 }
 
-// Merge of caller-provided partials (cross-GPU sequence split): part_o [nparts][R][D], part_m (natural log) / part_l
-// [nparts][R]; one block per row, D/4 threads.
+// Merge of caller-provided partials (cross-GPU sequence split): part s has O [R][D] at po + s * so, m (natural log) [R] at
+// pm + s * sm and l [R] at pl + s * sm (strides in floats); one block per row, D/4 threads.
 __global__ void merge_parts_k(const float * __restrict__ po, const float * __restrict__ pm, const float * __restrict__ pl,
-                              int nparts, int R, int D, const float * __restrict__ gate, float * __restrict__ out) {
+                              int nparts, int R, int D, const float * __restrict__ gate, float * __restrict__ out, size_t so,
+                              size_t sm) {
     const int r = blockIdx.x, i = threadIdx.x;
     float M = B200_NEG_INF;
-    for (int s = 0; s < nparts; ++s) M = fmaxf(M, pm[(size_t) s * R + r]);
+    for (int s = 0; s < nparts; ++s) M = fmaxf(M, pm[s * sm + r]);
     float den = 0.0f;
     float4 num = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     for (int s = 0; s < nparts; ++s) {
-        const float ms = pm[(size_t) s * R + r];
+        const float ms = pm[s * sm + r];
         if (ms == B200_NEG_INF) continue;
         const float f = ex2f((ms - M) * LOG2E);
-        den = fmaf(f, pl[(size_t) s * R + r], den);
-        const float4 o = reinterpret_cast<const float4 *>(po + ((size_t) s * R + r) * D)[i];
+        den = fmaf(f, pl[s * sm + r], den);
+        const float4 o = reinterpret_cast<const float4 *>(po + s * so + (size_t) r * D)[i];
         num.x = fmaf(f, o.x, num.x); num.y = fmaf(f, o.y, num.y); num.z = fmaf(f, o.z, num.z); num.w = fmaf(f, o.w, num.w);
     }
     float4 y = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
@@ -639,6 +655,8 @@ float * scratch_for(cudaStream_t s, size_t floats) {
 // ---- tensor maps of the cache ----------------------------------------------------------------------------------
 // K and V as rank-3 tensors of 16-bit elements: x = the row of one position (all kv heads), y = position inside a page
 // (or in the whole cache when it is contiguous), z = page.  The box is one head's bytes of 64 consecutive positions.
+// f16 rows (512 B per head) are wider than a box may be, and their shared-memory image is swizzled: rank 4 with x = 64
+// elements (128 B), y = position, z = 128-byte chunk of the row, w = page; box = 64 x 64 x 4 chunks, 128-byte swizzle.
 using encode_tiled_fn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                      const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                      CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -678,13 +696,23 @@ bool make_cache_map(CUtensorMap * m, const char * base, const dec_args & a, int 
             }
         }
     }
-    const cuuint64_t gdim[3] = {a.g.rowb / 2, rows, paged ? (cuuint64_t) 0x7fffffff : 1};
-    const cuuint64_t gstr[2] = {a.g.rowb, paged ? a.g.pstride : a.g.rowb * rows};
-    const cuuint32_t box[3] = {(cuuint32_t) HB / 2, (cuuint32_t) TILE, 1};
-    const cuuint32_t estr[3] = {1, 1, 1};
-    if (enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, (void *) base, gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return false;
+    const cuuint64_t npages = paged ? (cuuint64_t) 0x7fffffff : 1, pbytes = paged ? a.g.pstride : a.g.rowb * rows;
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult rc;
+    if (HB == head_bytes(B200_KV_F16)) {
+        const cuuint64_t gdim[4] = {64, rows, a.g.rowb / 128, npages};
+        const cuuint64_t gstr[3] = {a.g.rowb, 128, pbytes};
+        const cuuint32_t box[4] = {64, (cuuint32_t) TILE, 4, 1};
+        rc = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, (void *) base, gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else {
+        const cuuint64_t gdim[3] = {a.g.rowb / 2, rows, npages};
+        const cuuint64_t gstr[2] = {a.g.rowb, pbytes};
+        const cuuint32_t box[3] = {(cuuint32_t) HB / 2, (cuuint32_t) TILE, 1};
+        rc = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, (void *) base, gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                 CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
+    if (rc != CUDA_SUCCESS) return false;
     std::lock_guard<std::mutex> lk(g_map_mu);
     map_entry & e = g_maps[g_map_next];
     g_map_next = (g_map_next + 1) % MAP_CACHE;
@@ -706,7 +734,7 @@ int launch_part(const dec_args & a_in, dim3 grid, cudaStream_t s) {
     // tiled copies need a tile inside one page (pages of at least 64 rows), 16-byte row strides and a contiguous cache short
     // enough for the stride field; anything else keeps the row-by-row copies
     a.tiled = 0;
-    if (KT != B200_KV_F16 && (!a.g.pt || a.g.psh >= 6) && a.g.rowb % 16 == 0 &&
+    if ((!a.g.pt || a.g.psh >= 6) && a.g.rowb % 16 == 0 &&
         (a.g.pt ? a.g.pstride < ((unsigned long long) 1 << 40) : (a.n_ctx >= 1 && a.g.rowb * (unsigned long long) a.n_ctx < ((unsigned long long) 1 << 40))))
         a.tiled = make_cache_map(&mapK, a.g.k, a, traits<KT>::HB) && make_cache_map(&mapV, a.g.v, a, traits<KT>::HB);
     // as many CTAs per SM as the kernel is compiled for, if a ring of two half-tile slots fits that often into the 227 KB of
@@ -945,9 +973,40 @@ int b200_attn_merge_gate(const float * part_o, const float * part_m, const float
     if (!part_o || !part_m || !part_l || !out || nparts < 1 || R < 1 || D % 4 || D < 4 || D > 4096 || !aligned16(part_o) ||
         !aligned16(out) || (gate && !aligned16(gate)))
         B200_REFUSE(B200_ERR_SHAPE, "attn_merge_gate: unsupported arguments");
-    merge_parts_k<<<R, D / 4, 0, (cudaStream_t) stream>>>(part_o, part_m, part_l, nparts, R, D, gate, out);
+    merge_parts_k<<<R, D / 4, 0, (cudaStream_t) stream>>>(part_o, part_m, part_l, nparts, R, D, gate, out, (size_t) R * D, (size_t) R);
     count_launch();
     return launch_status("attn_merge_gate");
+}
+
+// The exchange step of the sequence split for a host that drives NCCL itself.  ncclAllGather is taken from the NCCL library
+// the process has already loaded (the host's own, or the one bundled with its framework), so the communicator and the
+// function come from the same library; nothing here links NCCL.
+int b200_seq_exchange_merge(void * nccl_comm, int n_seq, const float * send, float * recv, int R, int D, const float * gate,
+                            float * out, void * stream) {
+    using allgather_fn = int (*)(const void *, void *, size_t, int, void *, cudaStream_t);
+    static allgather_fn allgather = [] {
+        void * f = dlsym(RTLD_DEFAULT, "ncclAllGather");
+        if (!f) {
+            void * h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+            if (h) f = dlsym(h, "ncclAllGather");
+        }
+        return (allgather_fn) f;
+    }();
+    const size_t part = (size_t) R * (D + 2);
+    if (!send || !recv || !out || n_seq < 1 || R < 1 || D % 4 || D < 4 || D > 4096 || part % 4 || !aligned16(send) || !aligned16(recv) ||
+        !aligned16(out) || (gate && !aligned16(gate)) || (n_seq > 1 && !nccl_comm))
+        B200_REFUSE(B200_ERR_SHAPE, "seq_exchange_merge: unsupported arguments (R * (D + 2) must be a multiple of 4, buffers 16-byte aligned)");
+    cudaStream_t s = (cudaStream_t) stream;
+    const float * parts = send;
+    if (n_seq > 1) {
+        if (!allgather) B200_REFUSE(B200_ERR_CUDA, "seq_exchange_merge: no NCCL library is loaded in this process");
+        const int rc = allgather(send, recv, part, 7 /* ncclFloat32 */, nccl_comm, s);
+        if (rc != 0) B200_REFUSE(B200_ERR_CUDA, "seq_exchange_merge: ncclAllGather returned %d", rc);
+        parts = recv;
+    }
+    merge_parts_k<<<R, D / 4, 0, s>>>(parts, parts + (size_t) R * D, parts + (size_t) R * D + R, n_seq, R, D, gate, out, part, part);
+    count_launch();
+    return launch_status("seq_exchange_merge");
 }
 
 }  // extern "C"

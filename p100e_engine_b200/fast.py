@@ -103,6 +103,12 @@ def attn_merge_gate(part_o, part_m, part_l, nparts, R, D, gate, out, s=None):
                                          L.ptr(out), _stream(s)) == L.OK
 
 
+def seq_exchange_merge(nccl_comm, n_seq, send, recv, R, D, gate, out, s=None):
+    """all-gather of the shards' flat partials over the caller's ncclComm_t (an integer address) + merge + gate"""
+    return L.load().b200_seq_exchange_merge(C.c_void_p(nccl_comm), n_seq, L.ptr(send), L.ptr(recv), R, D, L.ptr(gate),
+                                            L.ptr(out), _stream(s)) == L.OK
+
+
 def attn_prefill(q, c, out, T, p0, Hq, scale, s=None):
     return L.load().b200_attn_prefill(L.ptr(q), C.byref(c.c()), L.ptr(out), T, p0, Hq, scale, _stream(s)) == L.OK
 

@@ -58,6 +58,7 @@ SIGNATURES = {
     "b200_attn_decode_slots_noalloc": (I, [P, KVP, P, P, I, I, P, I, I, F, I, P]),
     "b200_attn_decode_slots_partial": (I, [P, KVP, P, P, P, I, I, P, I, I, F, I, P]),
     "b200_attn_merge_gate": (I, [P, P, P, I, I, I, P, P, P]),
+    "b200_seq_exchange_merge": (I, [P, I, P, P, I, I, P, P, P]),
     "b200_attn_chunk_keys": (I, []),
     "b200_attn_prefill": (I, [P, KVP, P, I, I, I, F, P]),
     "b200_attn_prefill_variant": (I, [P, KVP, P, I, I, I, F, P, I]),

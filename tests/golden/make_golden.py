@@ -116,4 +116,4 @@ if __name__ == "__main__":
     if sys.argv[1] == "cpu":
         make_cpu()
     else:
-        make_gpu(sys.argv[2] if len(sys.argv) > 2 else os.path.join(ROOT, "gpurun_out"))
+        make_gpu(sys.argv[2] if len(sys.argv) > 2 else os.path.join(ROOT, "tests", "golden"))

@@ -55,6 +55,30 @@ def main():
     torch.cuda.synchronize()
     assert fast.device_status() == 0
     util.check_close(out.cpu().numpy().reshape(rows, hq, 256), want, "rank %d" % rank)
+    # the same step through the C entry point with a raw ncclComm_t, as a C++ host would drive it
+    import ctypes as C
+    path = [ln.split()[-1] for ln in open("/proc/self/maps") if "libnccl" in ln][0]
+    nccl = C.CDLL(path)
+
+    class UniqueId(C.Structure):
+        _fields_ = [("internal", C.c_byte * 128)]
+
+    uid = UniqueId()
+    if rank == 0:
+        assert nccl.ncclGetUniqueId(C.byref(uid)) == 0
+    t = torch.frombuffer(bytearray(bytes(uid)), dtype=torch.uint8).to(dev)
+    dist.broadcast(t, 0)
+    C.memmove(C.byref(uid), bytes(t.cpu().numpy().tobytes()), 128)
+    comm = C.c_void_p()
+    nccl.ncclCommInitRank.argtypes = [C.POINTER(C.c_void_p), C.c_int, UniqueId, C.c_int]
+    assert nccl.ncclCommInitRank(C.byref(comm), world, uid, rank) == 0
+    recv = torch.zeros(world, mg.send.numel(), device=dev)
+    out2 = torch.zeros_like(out)
+    assert fast.seq_exchange_merge(comm.value, world, mg.send, recv, rows * hq, 256, util.to_dev(gate, dev), out2)
+    torch.cuda.synchronize()
+    assert torch.equal(out, out2), "C exchange differs from the torch.distributed exchange"
+    nccl.ncclCommDestroy.argtypes = [C.c_void_p]
+    nccl.ncclCommDestroy(comm)
     dist.barrier()
     dist.destroy_process_group()
     print("OK rank", rank)

@@ -53,7 +53,7 @@ def test_decode_vs_oracle_depths(cuda, lib, tname):
 
 @pytest.mark.parametrize("tname", ["q8_0", "f16", "q4_0"])
 def test_decode_config1_vs_oracle_and_reference(cuda, lib, tname):
-    """BASELINE config 1 shape: one slot, q_len 1, context 4096, 16 pages of 256 in a seeded permutation, sigmoid gate;
+    """Single-sequence decode shape: one slot, q_len 1, context 4096, 16 pages of 256 in a seeded permutation, sigmoid gate;
     also against the reference's attn_decode on the same paged cache"""
     import torch
     from p100e_engine_b200 import fast
@@ -174,6 +174,34 @@ def test_paged_equals_contiguous_and_rows(cuda, lib, tname, interleave):
     assert fast.device_status() == 0
 
 
+@pytest.mark.parametrize("tname", ["q8_0", "f16", "q4_0"])
+def test_small_pages_take_the_row_copies(cuda, lib, tname):
+    """pages of 16 rows cannot hold a 64-row box, so such a pool is staged row by row through registers instead of by
+    tiled copies: the result must equal the contiguous cache (tiled copies) bitwise"""
+    import torch
+    from p100e_engine_b200 import fast
+    kt = TYPES[tname]
+    Hkv, Hq, n, psh, maxp = 2, 12, 1000, 4, 64
+    pool = util.PagedPool(kt, 80, psh=psh, hkv=Hkv, seed=21)
+    pt_t = util.to_dev(pool.take(n, maxp), cuda)
+    pool_t = torch.zeros(pool.bytes, dtype=torch.uint8, device=cuda)
+    k = util.to_dev(util.rng_normal(81, (n, Hkv, D)), cuda)
+    v = util.to_dev(util.rng_normal(82, (n, Hkv, D)), cuda)
+    cc = fast.kv_alloc(kt, maxp << psh, Hkv, D)
+    pc = util.dev_cache(pool_t, pool, pt_t, None, maxp << psh)
+    assert fast.kv_append(cc, k, v, 0, n) and fast.kv_append(pc, k, v, 0, n)
+    q = util.to_dev(util.rng_normal(83, (4, Hq, D)), cuda)
+    o1 = torch.zeros(4, Hq, D, device=cuda)
+    o2 = torch.zeros(4, Hq, D, device=cuda)
+    for T in (1, 4):
+        for p0 in (0, 15, 16, 63, 64, 500, n - T):
+            assert fast.attn_decode(q, cc, o1, T, p0, Hq, SCALE)
+            assert fast.attn_decode(q, pc, o2, T, p0, Hq, SCALE)
+            torch.cuda.synchronize()
+            assert torch.equal(o1[:T], o2[:T]), "small pages differ (T=%d p0=%d)" % (T, p0)
+    assert fast.device_status() == 0
+
+
 def _verify_batch(cuda, kt, n_slots, q_len, lens, seed, chunk_keys, gate_on=True):
     """config-2 style batch: slots with their own contexts in a shared pool; returns (got, oracle)"""
     import torch
@@ -212,7 +240,7 @@ def _verify_batch(cuda, kt, n_slots, q_len, lens, seed, chunk_keys, gate_on=True
 @pytest.mark.parametrize("tname", ["q8_0", "f16", "q4_0"])
 @pytest.mark.parametrize("chunk", [0, 256, -1])
 def test_verify_batch_vs_oracle(cuda, lib, tname, chunk):
-    """BASELINE config 2 shape at oracle-friendly sizes: 8 slots x q_len 4, ragged contexts, shared pool, gate"""
+    """MTP-verify batch shape at oracle-friendly sizes: 8 slots x q_len 4, ragged contexts, shared pool, gate"""
     lens = [1024, 3000, 257, 4, 640, 2049, 1500, 511]
     got, ref, _ = _verify_batch(cuda, TYPES[tname], 8, 4, lens, 3, chunk)
     util.check_close(got, ref, "verify batch %s chunk=%d" % (tname, chunk))

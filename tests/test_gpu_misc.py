@@ -1,6 +1,6 @@
 """Further GPU parity cases: interleaved M-RoPE in attn_prep (reference tests/mrope_test.cu:62-117), the gate / a16
 epilogue (tests/fast_fusion_test.cu:161-178, tests/fast_fused_test.cu:100), offsets beyond 4 GiB (the reference's 32-bit
-limit, src/fast/attn_dec2.cu:495), BASELINE config 4 at full size (16 slots x 131072 keys, q4_0), and the two-GPU
+limit, src/fast/attn_dec2.cu:495), the long-context q4_0 batch at full size (16 slots x 131072 keys, q4_0), and the two-GPU
 sequence split through NCCL when two GPUs are present."""
 import ctypes as C
 import os
@@ -117,7 +117,7 @@ def test_offsets_beyond_4gib(cuda, lib):
 
 
 def test_config4_full_size_q4_0(cuda, lib):
-    """BASELINE config 4: 16 slots x 131072 keys, q4_0, 512 pages per slot in a seeded permutation of an 8192-page pool.
+    """Long-context batch: 16 slots x 131072 keys, q4_0, 512 pages per slot in a seeded permutation of an 8192-page pool.
     Two slots are checked against the oracle; all slots through chunk independence (two chunk sizes agree)."""
     import torch
     from p100e_engine_b200 import fast

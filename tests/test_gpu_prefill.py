@@ -109,7 +109,7 @@ def test_prefill_equals_looped_decode(cuda, lib):
 
 
 def test_prefill_linearity_in_v_full_size(cuda, lib):
-    """BASELINE config 3 at full size (T = 8192, p0 = 0, q8_0, 32 pages): too large for the oracle, so checked through
+    """Chunked-prefill shape at full size (T = 8192, p0 = 0, q8_0, 32 pages): too large for the oracle, so checked through
     size-independent properties: rows of a chunked call (4 x 2048 with growing p0) equal the single call, and the
     first rows equal a short prefix run"""
     import torch

@@ -7,7 +7,7 @@ HQ, HKV, D = 24, 4, 256
 SCALE = 1.0 / 16.0
 TYPES = {"f16": 1, "q4_0": 2, "q8_0": 8}
 
-# Tolerance for fp32-accumulated attention outputs (the BASELINE bar "max-abs 2e-3 / rel 1e-2"), measured the way the
+# Tolerance for fp32-accumulated attention outputs (the bar "max-abs 2e-3 / rel 1e-2"), measured the way the
 # reference's own tests measure: largest absolute error relative to the largest reference magnitude
 # (max_abs <= 2e-3 * max|ref|, tests/fast_attn_test.cu:70-78 in the reference project) and relative RMS error
 # (rel-RMS <= 1e-2, tests/fast_attn_fold_test.cu:82).
