@@ -45,6 +45,7 @@ constexpr int SDSTR = 132;            // bytes per V-scale row (64 f16 + 4)
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 constexpr float PSHIFT = 8.0f;        // P (and l) are kept times 2^8 inside the kernels
+constexpr float REF_GAP = 7.0f;       // a row's reference maximum may trail its true maximum by this much (log2 units)
 
 template <uint32_t KT> struct traits {
     static constexpr int HB = head_bytes(KT);                       // bytes of a head row in the cache
@@ -374,7 +375,9 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
             for (int e = 0; e < 2; ++e) {
                 const int r = 8 * i + 2 * t + e;
                 float mx = fmaxf(fmaxf(wmax[r], wmax[NT * 8 + r]), fmaxf(wmax[2 * NT * 8 + r], wmax[3 * NT * 8 + r]));
-                const float mnew = fmaxf(m_run[i][e], mx);
+                // the reference maximum moves only when the tile maximum leaves the headroom f16 gives P (P <= 2^(8 + 7)):
+                // most tiles then need no rescale of the running output at all
+                const float mnew = mx > m_run[i][e] + REF_GAP ? mx : m_run[i][e];
                 const float msafe = mnew == B200_NEG_INF ? 0.0f : mnew;
                 fsc[i][e] = ex2f(m_run[i][e] - msafe);
                 m_run[i][e] = mnew;
