@@ -551,10 +551,10 @@ __global__ void __launch_bounds__(64) decode_merge_k(const dec_args a, const flo
     for (int c = 0; c < nch; ++c) M = fmaxf(M, a.pm[(unit0 + c) * R + r]);
     float den = 0.0f;
     float4 num = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    for (int c = 0; c < nch; ++c) {
+#pragma unroll 4
+    for (int c = 0; c < nch; ++c) {   // no early continue: the loads of several chunks are in flight together
         const float ms = a.pm[(unit0 + c) * R + r];
-        if (ms == B200_NEG_INF) continue;
-        const float f = ex2f(ms - M);
+        const float f = ms == B200_NEG_INF ? 0.0f : ex2f(ms - M);   // a chunk the row did not see holds zeros: adds nothing
         den = fmaf(f, a.pl[(unit0 + c) * R + r], den);
         const float4 o = reinterpret_cast<const float4 *>(a.po + ((unit0 + c) * R + r) * DH)[threadIdx.x];
         num.x = fmaf(f, o.x, num.x); num.y = fmaf(f, o.y, num.y); num.z = fmaf(f, o.z, num.z); num.w = fmaf(f, o.w, num.w);
