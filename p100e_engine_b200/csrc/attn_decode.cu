@@ -220,10 +220,9 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
             const int j = r / GQA, hh = r - j * GQA;
             v = *reinterpret_cast<const float4 *>(a.q + ((size_t) (slot * a.q_len + j) * a.Hq + hk * GQA + hh) * DH + d4);
         }
-        const float vv[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e)
-            *reinterpret_cast<__half *>(Qs + r * QSTR + q_slot<KT>(d4 + e) * 2) = __float2half_rn(vv[e] * a.qscale);
+        // four consecutive dims stay consecutive under q_slot (it permutes groups of four): one 8-byte store
+        *reinterpret_cast<uint2 *>(Qs + r * QSTR + q_slot<KT>(d4) * 2) =
+            make_uint2(pack_h2(v.x * a.qscale, v.y * a.qscale), pack_h2(v.z * a.qscale, v.w * a.qscale));
     }
     __syncthreads();
 
