@@ -10,8 +10,9 @@
 //             (all GQA heads and verify rows share one pass over the KV bytes).  int8 / nibbles are widened to f16
 //             exactly in registers (byte permute + one f16x2 subtract), products accumulate in fp32 on the tensor
 //             cores (mma.sync m16n8k16), the per-32 block scale multiplies the fp32 partial sums.
-//   softmax   online, per row, base 2; the tile maximum is exchanged through shared memory, P goes to shared memory
-//             as f16.
+//   softmax   online, per row, base 2, against a reference maximum that all warps share and that may trail the true
+//             maximum by 2^7: a tile whose scores stay under it needs one block barrier (P to shared memory as f16, then
+//             P V); only a tile that outgrows it makes the warps exchange maxima, redo P and rescale O.
 //   PV        warp w owns output dims 64w..64w+63: V^T tiles on M, rows on N, fp32 accumulators in registers.
 //   partials  each unit writes unnormalised (O, m, l); a merge kernel combines a row's chunks in chunk order, applies
 //             the optional sigmoid gate and normalises (reference formula: dec2_combine_k, src/fast/attn_dec2.cu:430-450).
@@ -138,6 +139,7 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
     // shared memory carve-up
     uint64_t * full = reinterpret_cast<uint64_t *>(smem);                    // [nslot]
     int * done = reinterpret_cast<int *>(smem + 96);                         // warps that finished Q K^T / P V (two counters)
+    int * flag = reinterpret_cast<int *>(smem + 104);                        // [3] "some warp's scores outgrew the references"
     int * pgs = reinterpret_cast<int *>(smem + 128);                         // [PGS] page-table entries of the chunk's pages
     unsigned char * stg = smem + HDR;                                        // nslot * SLOT
     unsigned char * Qs = stg + (size_t) nslot * TR::SLOT;                    // [NT*8][QSTR]
@@ -206,6 +208,7 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
             for (int s = 0; s < nslot; ++s) mbar_init(&full[s], 1);
             mbar_fence_init();
             done[0] = done[1] = 0;
+            flag[0] = flag[1] = flag[2] = 0;
         }
         __syncwarp();
         for (int q0 = 0; q0 < nslot; ++q0) issue(q0, q0, true);
@@ -353,6 +356,12 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
                     if (keyB > rpos[i][e] || keyB >= k_hi) S[i][2 + e] = B200_NEG_INF;
                 }
         }
+        // ---------------- online softmax, P -> shared memory ----------------
+        // Every row has a reference maximum m_run, the same in all four warps, that trails its true maximum by at most
+        // REF_GAP (P = 2^(S - m_run + PSHIFT) <= 2^15 stays inside f16).  A warp whose keys stay under m_run + REF_GAP needs
+        // nothing from the other warps: it writes P at once.  Only when some warp of the CTA sees a larger score (always on
+        // the first tile) do the warps exchange their maxima after the barrier, move the references, redo P and rescale O.
+        bool grow = false;
 #pragma unroll
         for (int i = 0; i < NT; ++i)
 #pragma unroll
@@ -362,32 +371,35 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
                 if (g == 0) wmax[w * NT * 8 + 8 * i + 2 * t + e] = mx;
+                grow = grow || mx > m_run[i][e] + REF_GAP;
             }
-        __syncthreads();   // B1: row maxima visible
+        const int ph = it % 3;   // three flags in turn: the one of the next tile is cleared two barriers after its last reader
+        if (__any_sync(0xffffffffu, grow) && lane == 0) flag[ph] = 1;
+        if (tid == 0) flag[ph == 2 ? 0 : ph + 1] = 0;
+        // P and the V scales of this tile replace those of the previous tile: every warp must be done with its P V
+        if (it > 0) {
+            int spins = 0;
+            while (*reinterpret_cast<volatile int *>(&done[1]) < NWARP * it)
+                if (++spins > (1 << 24)) { atomicOr(a.status, ST_WAIT_TIMEOUT); break; }
+        }
+        float lsum[NT][2];
+        auto write_p = [&]() {   // P carries a factor 2^PSHIFT (numerator and denominator alike): keeps small weights out of
+                                 // the f16 subnormal range; 2^(-inf) = 0 for a masked key
+#pragma unroll
+            for (int i = 0; i < NT; ++i)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int r = 8 * i + 2 * t + e;
+                    const float msafe = m_run[i][e] == B200_NEG_INF ? 0.0f : m_run[i][e];
+                    const __half pa = __float2half_rn(ex2f(S[i][e] - msafe + PSHIFT));
+                    const __half pb = __float2half_rn(ex2f(S[i][2 + e] - msafe + PSHIFT));
+                    lsum[i][e] = __half2float(pa) + __half2float(pb);
+                    *reinterpret_cast<__half *>(Ps + r * PSTR + kA * 2) = pa;
+                    *reinterpret_cast<__half *>(Ps + r * PSTR + kB * 2) = pb;
+                }
+        };
+        write_p();
         mbar_wait(bar_v, par_v, a.status);   // this tile's V rows
-
-        // ---------------- online softmax, P -> shared memory ----------------
-        float fsc[NT][2];
-#pragma unroll
-        for (int i = 0; i < NT; ++i)
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int r = 8 * i + 2 * t + e;
-                float mx = fmaxf(fmaxf(wmax[r], wmax[NT * 8 + r]), fmaxf(wmax[2 * NT * 8 + r], wmax[3 * NT * 8 + r]));
-                // the reference maximum moves only when the tile maximum leaves the headroom f16 gives P (P <= 2^(8 + 7)):
-                // most tiles then need no rescale of the running output at all
-                const float mnew = mx > m_run[i][e] + REF_GAP ? mx : m_run[i][e];
-                const float msafe = mnew == B200_NEG_INF ? 0.0f : mnew;
-                fsc[i][e] = ex2f(m_run[i][e] - msafe);
-                m_run[i][e] = mnew;
-                // P carries a factor 2^PSHIFT (numerator and denominator alike): keeps small weights out of the f16
-                // subnormal range
-                const __half pa = __float2half_rn(ex2f(S[i][e] - msafe + PSHIFT));       // 2^(-inf) = 0 for a masked key
-                const __half pb = __float2half_rn(ex2f(S[i][2 + e] - msafe + PSHIFT));
-                l_run[i][e] = fmaf(l_run[i][e], fsc[i][e], __half2float(pa) + __half2float(pb));
-                *reinterpret_cast<__half *>(Ps + r * PSTR + kA * 2) = pa;
-                *reinterpret_cast<__half *>(Ps + r * PSTR + kB * 2) = pb;
-            }
         if constexpr (TR::SCALED) {   // V block scales, transposed to [block][key]
             const int key = tid >> 1, b0 = (tid & 1) * 4;
 #pragma unroll
@@ -396,11 +408,24 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
                 *reinterpret_cast<uint16_t *>(Sd + b * SDSTR + key * 2) = *reinterpret_cast<const uint16_t *>(src);
             }
         }
-        // rescale the running output (the factors are exactly 1 while no row's maximum moves: skipped then)
-        bool moved = false;
+        __syncthreads();   // P, the V scales, the warps' maxima and the flag are visible
+        if (flag[ph]) {
+            float fsc[NT][2];
 #pragma unroll
-        for (int i = 0; i < NT; ++i) moved = moved || fsc[i][0] != 1.0f || fsc[i][1] != 1.0f;
-        if (__any_sync(0xffffffffu, moved)) {
+            for (int i = 0; i < NT; ++i)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int r = 8 * i + 2 * t + e;
+                    const float mx = fmaxf(fmaxf(wmax[r], wmax[NT * 8 + r]), fmaxf(wmax[2 * NT * 8 + r], wmax[3 * NT * 8 + r]));
+                    const float mnew = mx > m_run[i][e] + REF_GAP ? mx : m_run[i][e];
+                    fsc[i][e] = ex2f(m_run[i][e] - (mnew == B200_NEG_INF ? 0.0f : mnew));
+                    m_run[i][e] = mnew;
+                }
+            write_p();   // rows whose reference stayed get the same bits again
+#pragma unroll
+            for (int i = 0; i < NT; ++i)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) l_run[i][e] = fmaf(l_run[i][e], fsc[i][e], lsum[i][e]);
 #pragma unroll
             for (int mt = 0; mt < 4; ++mt)
 #pragma unroll
@@ -408,8 +433,13 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
                     O[mt][i][0] *= fsc[i][0]; O[mt][i][1] *= fsc[i][1];
                     O[mt][i][2] *= fsc[i][0]; O[mt][i][3] *= fsc[i][1];
                 }
+            __syncthreads();   // the rewritten P is visible
+        } else {
+#pragma unroll
+            for (int i = 0; i < NT; ++i)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) l_run[i][e] += lsum[i][e];
         }
-        __syncthreads();   // B2: P and the V scales are visible
 
         // ---------------- O^T += V^T P^T for the warp's 64 output dims ----------------
 #pragma unroll
