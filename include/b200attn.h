@@ -164,7 +164,9 @@ int b200_attn_merge_gate(const float *part_o, const float *part_m, const float *
  * reference twin).  send = this shard's partial as one flat buffer [O (R*D) | m (R) | l (R)] (the three outputs of
  * b200_attn_decode_slots_partial placed back to back), recv = n_seq such buffers.  ncclAllGather over `nccl_comm`
  * (an ncclComm_t of the n_seq shards, rank order = shard order) on `stream`, then the merge of b200_attn_merge_gate.
- * n_seq == 1 merges `send` alone.  NCCL is not linked: the symbol is taken from the NCCL library already loaded. */
+ * n_seq == 1 merges `send` alone; nccl_comm == NULL with n_seq > 1 means the caller has already gathered the n_seq
+ * buffers into recv (some other transport) and only the merge runs.  NCCL is not linked: the symbol is taken from the
+ * NCCL library already loaded. */
 int b200_seq_exchange_merge(void *nccl_comm, int n_seq, const float *send, float *recv, int R, int D, const float *gate,
                             float *out, void *stream);
 int b200_attn_chunk_keys(void); /* the default chunk (keys) used by the reference-compatible entry points */

@@ -1026,15 +1026,14 @@ int b200_seq_exchange_merge(void * nccl_comm, int n_seq, const float * send, flo
     }();
     const size_t part = (size_t) R * (D + 2);
     if (!send || !recv || !out || n_seq < 1 || R < 1 || D % 4 || D < 4 || D > 4096 || part % 4 || !aligned16(send) || !aligned16(recv) ||
-        !aligned16(out) || (gate && !aligned16(gate)) || (n_seq > 1 && !nccl_comm))
+        !aligned16(out) || (gate && !aligned16(gate)))
         B200_REFUSE(B200_ERR_SHAPE, "seq_exchange_merge: unsupported arguments (R * (D + 2) must be a multiple of 4, buffers 16-byte aligned)");
     cudaStream_t s = (cudaStream_t) stream;
-    const float * parts = send;
-    if (n_seq > 1) {
+    const float * parts = n_seq > 1 ? recv : send;
+    if (n_seq > 1 && nccl_comm) {   // without a communicator the caller has gathered the parts into recv already
         if (!allgather) B200_REFUSE(B200_ERR_CUDA, "seq_exchange_merge: no NCCL library is loaded in this process");
         const int rc = allgather(send, recv, part, 7 /* ncclFloat32 */, nccl_comm, s);
         if (rc != 0) B200_REFUSE(B200_ERR_CUDA, "seq_exchange_merge: ncclAllGather returned %d", rc);
-        parts = recv;
     }
     merge_parts_k<<<R, D / 4, 0, s>>>(parts, parts + (size_t) R * D, parts + (size_t) R * D + R, n_seq, R, D, gate, out, part, part);
     count_launch();

@@ -203,7 +203,7 @@ __global__ void prep_k(const TIN * __restrict__ qg, const TIN * __restrict__ k, 
     }
 }
 
-// The prefill path over whole token rows (bf16 in, no norm): one block of 256 threads per token.  cos / sin of a rotary
+// The prefill path over whole token rows (bf16 in, no norm): one block of ROPE_THR threads per token.  cos / sin of a rotary
 // pair depend on the token and the pair only, so they are computed once per token instead of once per head (same
 // expressions, same values); q rows move as 16-byte loads / 32-byte stores; the K heads are rotated in shared memory and
 // every warp then quantises 32-value blocks of K and V.  Needs n_rot % 16 == 0 and 16-byte aligned rows.
@@ -212,20 +212,23 @@ __device__ __forceinline__ void bf16x8_to_f32(const uint4 u, float (&f)[8]) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) { f[2 * e] = __uint_as_float(w[e] << 16); f[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u); }
 }
+#ifndef ROPE_THR
+#define ROPE_THR 128
+#endif
 template <uint32_t KT>
-__global__ void __launch_bounds__(256) rope_rows_k(const __nv_bfloat16 * __restrict__ qg, const __nv_bfloat16 * __restrict__ k,
+__global__ void __launch_bounds__(ROPE_THR) rope_rows_k(const __nv_bfloat16 * __restrict__ qg, const __nv_bfloat16 * __restrict__ k,
                                                    const __nv_bfloat16 * __restrict__ v, float * __restrict__ q, kv_view g, int p0,
                                                    int Hq, int Hkv, int D, int n_rot, float freq_base, unsigned * status) {
     extern __shared__ float smr[];   // cos[half] | sin[half] | K heads [Hkv][D]
     const int t = blockIdx.x, i = threadIdx.x, half = n_rot / 2, lane = i & 31, wid = i >> 5, nb = D / 32;
     float * cs = smr, * kb = smr + n_rot;
     const int ppos = p0 + t;
-    for (int j = i; j < half; j += 256) {
+    for (int j = i; j < half; j += ROPE_THR) {
         const float theta = (float) ppos * powf(freq_base, -2.0f * j / n_rot);
         cs[j] = cosf(theta);
         cs[half + j] = sinf(theta);
     }
-    for (int e = i; e < Hkv * D / 8; e += 256) {
+    for (int e = i; e < Hkv * D / 8; e += ROPE_THR) {
         float f[8];
         bf16x8_to_f32(__ldg(reinterpret_cast<const uint4 *>(k + (size_t) t * Hkv * D) + e), f);
         reinterpret_cast<float4 *>(kb)[2 * e] = make_float4(f[0], f[1], f[2], f[3]);
@@ -234,7 +237,7 @@ __global__ void __launch_bounds__(256) rope_rows_k(const __nv_bfloat16 * __restr
     __syncthreads();
     if (qg) {
         const int PI = half / 8, IT = PI + (D - n_rot) / 8;   // per head: items of 8 rotary pairs, then items of 8 plain values
-        for (int it = i; it < Hq * IT; it += 256) {
+        for (int it = i; it < Hq * IT; it += ROPE_THR) {
             const int h = it / IT, r = it - h * IT;
             const __nv_bfloat16 * src = qg + ((size_t) t * Hq + h) * D;
             float * dst = q + ((size_t) t * Hq + h) * D;
@@ -261,7 +264,7 @@ __global__ void __launch_bounds__(256) rope_rows_k(const __nv_bfloat16 * __restr
             }
         }
     }
-    for (int e = i; e < Hkv * half; e += 256) {
+    for (int e = i; e < Hkv * half; e += ROPE_THR) {
         const int h = e / half, j = e - h * half;
         const float c = cs[j], sn = cs[half + j];
         rot_pair(kb[h * D + j], kb[h * D + j + half], c, sn, kb[h * D + j], kb[h * D + j + half]);
@@ -271,7 +274,7 @@ __global__ void __launch_bounds__(256) rope_rows_k(const __nv_bfloat16 * __restr
     const int32_t * tab = kv_tab(g, t);
     if (tab && tab[row >> g.psh] < 0) { if (i == 0) atomicOr(status, ST_BAD_PAGE); return; }
     const unsigned long long roff = kv_off_tab(g, tab, row);
-    for (int bb = wid; bb < Hkv * nb; bb += 8) {
+    for (int bb = wid; bb < Hkv * nb; bb += ROPE_THR / 32) {
         const int h = bb / nb, b = bb - h * nb;
         const unsigned long long ho = roff + (unsigned long long) h * head_bytes(KT, D);
         store_block_warp<KT>(kb[bb * 32 + lane], lane, g.k + ho, b, nb);
@@ -490,9 +493,9 @@ int b200_rope_append_bf16(const uint16_t * q, const uint16_t * k, const uint16_t
         const kv_view g = view_of(*c);
         const __nv_bfloat16 * qb = (const __nv_bfloat16 *) q, * kb = (const __nv_bfloat16 *) k, * vb = (const __nv_bfloat16 *) v;
         cudaStream_t s = (cudaStream_t) stream;
-        if (c->type == B200_KV_F16) rope_rows_k<B200_KV_F16><<<T, 256, smem, s>>>(qb, kb, vb, q_out, g, p0, Hq, Hkv, D, n_rot, freq_base, st);
-        else if (c->type == B200_KV_Q8_0) rope_rows_k<B200_KV_Q8_0><<<T, 256, smem, s>>>(qb, kb, vb, q_out, g, p0, Hq, Hkv, D, n_rot, freq_base, st);
-        else rope_rows_k<B200_KV_Q4_0><<<T, 256, smem, s>>>(qb, kb, vb, q_out, g, p0, Hq, Hkv, D, n_rot, freq_base, st);
+        if (c->type == B200_KV_F16) rope_rows_k<B200_KV_F16><<<T, ROPE_THR, smem, s>>>(qb, kb, vb, q_out, g, p0, Hq, Hkv, D, n_rot, freq_base, st);
+        else if (c->type == B200_KV_Q8_0) rope_rows_k<B200_KV_Q8_0><<<T, ROPE_THR, smem, s>>>(qb, kb, vb, q_out, g, p0, Hq, Hkv, D, n_rot, freq_base, st);
+        else rope_rows_k<B200_KV_Q4_0><<<T, ROPE_THR, smem, s>>>(qb, kb, vb, q_out, g, p0, Hq, Hkv, D, n_rot, freq_base, st);
         count_launch();
         return launch_status("rope_append_bf16");
     }

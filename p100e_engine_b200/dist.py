@@ -62,9 +62,6 @@ class SeqMerge:
         # one flat send buffer per rank: [O (R*d) | m (R) | l (R)], gathered into [n_seq][R*(d+2)]
         self.send = torch.zeros(R * (d + 2), dtype=torch.float32, device=device)
         self.recv = torch.zeros(plan.n_seq, R * (d + 2), dtype=torch.float32, device=device)
-        self.po = torch.zeros(plan.n_seq, R, d, dtype=torch.float32, device=device)
-        self.pm = torch.zeros(plan.n_seq, R, dtype=torch.float32, device=device)
-        self.pl = torch.zeros(plan.n_seq, R, dtype=torch.float32, device=device)
 
     def views(self):
         """(part_o, part_m, part_l) views of the send buffer for b200_attn_decode_slots_partial"""
@@ -76,11 +73,9 @@ class SeqMerge:
         from . import fast
         R, d = self.R, self.d
         dist.all_gather_into_tensor(self.recv.view(-1), self.send, group=self.group)
-        self.po.copy_(self.recv[:, :R * d].reshape(self.plan.n_seq, R, d))
-        self.pm.copy_(self.recv[:, R * d:R * d + R])
-        self.pl.copy_(self.recv[:, R * d + R:])
-        if not fast.attn_merge_gate(self.po, self.pm, self.pl, self.plan.n_seq, R, d, gate, out):
-            raise RuntimeError("attn_merge_gate refused")
+        # the merge reads the gathered flat buffers in place (no communicator: the gather above was the exchange)
+        if not fast.seq_exchange_merge(0, self.plan.n_seq, self.send, self.recv, R, d, gate, out):
+            raise RuntimeError("seq_exchange_merge refused")
 
 
 def merge_partials_host(parts_o, parts_m, parts_l):

@@ -162,3 +162,35 @@ def test_two_gpu_sequence_split_nccl(cuda, lib):
                         "127.0.0.1", "--master-port", "29533", os.path.join(ROOT, "tests", "nccl_seq_split_worker.py")],
                        env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and r.stdout.count("OK") == 2, r.stdout + r.stderr
+
+
+def test_seq_exchange_merge_single_shard(cuda, lib):
+    """with one sequence shard the exchange entry point needs no communicator: it normalises and gates the flat partial
+    exactly as attn_merge_gate does with one part"""
+    import torch
+    from p100e_engine_b200 import fast
+    R, Dm = 24, 256
+    rng = np.random.default_rng(5)
+    po = torch.from_numpy(rng.standard_normal((R, Dm)).astype(np.float32)).to(cuda)
+    pm = torch.from_numpy(rng.standard_normal(R).astype(np.float32)).to(cuda)
+    pl = torch.from_numpy((rng.random(R) + 0.5).astype(np.float32)).to(cuda)
+    pm[3] = float("-inf")   # a row that saw no key
+    pl[3] = 0.0
+    gate = torch.from_numpy(rng.standard_normal((R, Dm)).astype(np.float32)).to(cuda)
+    send = torch.cat([po.reshape(-1), pm, pl]).contiguous()
+    recv = torch.zeros_like(send)
+    o1 = torch.zeros(R, Dm, device=cuda)
+    o2 = torch.zeros(R, Dm, device=cuda)
+    assert fast.attn_merge_gate(po, pm, pl, 1, R, Dm, gate, o1)
+    assert fast.seq_exchange_merge(0, 1, send, recv, R, Dm, gate, o2)
+    torch.cuda.synchronize()
+    assert torch.equal(o1, o2)
+    assert torch.all(o2[3] == 0)
+    want = po.cpu().numpy() / pl.cpu().numpy()[:, None] / (1.0 + np.exp(-gate.cpu().numpy()))
+    want[3] = 0
+    np.testing.assert_allclose(o2.cpu().numpy(), want, rtol=2e-5, atol=1e-6)
+    # two shards gathered by the caller (no communicator): the same part twice merges to the same rows
+    recv2 = torch.cat([send, send]).contiguous()
+    assert fast.seq_exchange_merge(0, 2, send, recv2, R, Dm, gate, o2)
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(o2.cpu().numpy(), want, rtol=2e-5, atol=1e-6)
