@@ -234,34 +234,37 @@ __global__ void __launch_bounds__(ROPE_THR) rope_rows_k(const __nv_bfloat16 * __
         reinterpret_cast<float4 *>(kb)[2 * e] = make_float4(f[0], f[1], f[2], f[3]);
         reinterpret_cast<float4 *>(kb)[2 * e + 1] = make_float4(f[4], f[5], f[6], f[7]);
     }
+    // the dims past n_rot of every q head are converted and copied first: they need no cos / sin, so this traffic (most of the
+    // row) runs while the first warp is still busy with the trigonometry
+    const int PI = half / 8, CI = (D - n_rot) / 8;   // per head: items of 8 rotary pairs, items of 8 plain values
+    if (qg) {
+        for (int it = i; it < Hq * CI; it += ROPE_THR) {
+            const int h = it / CI, d0 = n_rot + (it - h * CI) * 8;
+            float a[8];
+            bf16x8_to_f32(__ldg(reinterpret_cast<const uint4 *>(qg + ((size_t) t * Hq + h) * D + d0)), a);
+            float * dst = q + ((size_t) t * Hq + h) * D + d0;
+            reinterpret_cast<float4 *>(dst)[0] = make_float4(a[0], a[1], a[2], a[3]);
+            reinterpret_cast<float4 *>(dst)[1] = make_float4(a[4], a[5], a[6], a[7]);
+        }
+    }
     __syncthreads();
     if (qg) {
-        const int PI = half / 8, IT = PI + (D - n_rot) / 8;   // per head: items of 8 rotary pairs, then items of 8 plain values
-        for (int it = i; it < Hq * IT; it += ROPE_THR) {
-            const int h = it / IT, r = it - h * IT;
+        for (int it = i; it < Hq * PI; it += ROPE_THR) {
+            const int h = it / PI, d0 = (it - h * PI) * 8;
             const __nv_bfloat16 * src = qg + ((size_t) t * Hq + h) * D;
             float * dst = q + ((size_t) t * Hq + h) * D;
-            if (r < PI) {
-                const int d0 = r * 8;
-                float a[8], b[8], y0[8], y1[8];
-                bf16x8_to_f32(__ldg(reinterpret_cast<const uint4 *>(src + d0)), a);
-                bf16x8_to_f32(__ldg(reinterpret_cast<const uint4 *>(src + d0 + half)), b);
+            float a[8], b[8], y0[8], y1[8];
+            bf16x8_to_f32(__ldg(reinterpret_cast<const uint4 *>(src + d0)), a);
+            bf16x8_to_f32(__ldg(reinterpret_cast<const uint4 *>(src + d0 + half)), b);
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const float c = cs[d0 + e], sn = cs[half + d0 + e];
-                    rot_pair(a[e], b[e], c, sn, y0[e], y1[e]);
-                }
-                reinterpret_cast<float4 *>(dst + d0)[0] = make_float4(y0[0], y0[1], y0[2], y0[3]);
-                reinterpret_cast<float4 *>(dst + d0)[1] = make_float4(y0[4], y0[5], y0[6], y0[7]);
-                reinterpret_cast<float4 *>(dst + d0 + half)[0] = make_float4(y1[0], y1[1], y1[2], y1[3]);
-                reinterpret_cast<float4 *>(dst + d0 + half)[1] = make_float4(y1[4], y1[5], y1[6], y1[7]);
-            } else {
-                const int d0 = n_rot + (r - PI) * 8;
-                float a[8];
-                bf16x8_to_f32(__ldg(reinterpret_cast<const uint4 *>(src + d0)), a);
-                reinterpret_cast<float4 *>(dst + d0)[0] = make_float4(a[0], a[1], a[2], a[3]);
-                reinterpret_cast<float4 *>(dst + d0)[1] = make_float4(a[4], a[5], a[6], a[7]);
+            for (int e = 0; e < 8; ++e) {
+                const float c = cs[d0 + e], sn = cs[half + d0 + e];
+                rot_pair(a[e], b[e], c, sn, y0[e], y1[e]);
             }
+            reinterpret_cast<float4 *>(dst + d0)[0] = make_float4(y0[0], y0[1], y0[2], y0[3]);
+            reinterpret_cast<float4 *>(dst + d0)[1] = make_float4(y0[4], y0[5], y0[6], y0[7]);
+            reinterpret_cast<float4 *>(dst + d0 + half)[0] = make_float4(y1[0], y1[1], y1[2], y1[3]);
+            reinterpret_cast<float4 *>(dst + d0 + half)[1] = make_float4(y1[4], y1[5], y1[6], y1[7]);
         }
     }
     for (int e = i; e < Hkv * half; e += ROPE_THR) {
