@@ -229,11 +229,16 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
     }
     __syncthreads();
 
-    // consumed(c, q, s): this warp is done with item q in slot s; the last of the four warps refills the slot
-    auto consumed = [&](int c, int q, int s) {
+    // arrive(c): this warp is done with the K (c = 0) or V (c = 1) item of the tile; lane 0 learns whether it was the last of
+    // the four warps.  refill_if_last: that warp refills the slot.  The two are apart in the instruction stream so that the
+    // round trip of the shared-memory atomic is covered by other work.
+    auto arrive = [&](int c) {
         asm volatile("" ::: "memory");   // the item's shared-memory reads stay above this point
         int last = 0;
         if (lane == 0) last = (atomicAdd(&done[c], 1) & (NWARP - 1)) == NWARP - 1;
+        return last;
+    };
+    auto refill_if_last = [&](int last, int q, int s) {
         if (__shfl_sync(0xffffffffu, last, 0)) issue(q + nslot, s, false);
     };
 
@@ -263,6 +268,7 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
     const int mask_from = min(k_hi, rmin + 1);
 
     // ring position of the tile's K item (2 it) and V item (2 it + 1): slot index and the parity of its use count
+    int last_v = 0, sv_prev = 0;
     int sk = 0, sv = 1 % nslot;
     uint32_t phk = 0, phv = nslot == 1 ? 1u : 0u;
     for (int it = 0; it < ntiles; ++it) {
@@ -274,6 +280,7 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
         sk += 2; if (sk >= nslot) { sk -= nslot; phk ^= 1u; }
         sv += 2; if (sv >= nslot) { sv -= nslot; phv ^= 1u; }
         mbar_wait(bar_k, par_k, a.status);
+        if (it > 0) refill_if_last(last_v, 2 * it - 1, sv_prev);   // the V slot of the previous tile
 
         // ---------------- S = K Q^T for the warp's 16 keys ----------------
         float S[NT][4];
@@ -344,7 +351,7 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
                 }
             }
         }
-        consumed(0, 2 * it, sk_now);
+        const int last_k = arrive(0);
         // causal / chunk mask, warp-level row maxima
         const int keyA = k_lo + it * TILE + kA, keyB = keyA + 8;
         if (k_lo + (it + 1) * TILE > mask_from) {
@@ -365,17 +372,11 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
 #pragma unroll
         for (int i = 0; i < NT; ++i)
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                float mx = fmaxf(S[i][e], S[i][2 + e]);
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-                if (g == 0) wmax[w * NT * 8 + 8 * i + 2 * t + e] = mx;
-                grow = grow || mx > m_run[i][e] + REF_GAP;
-            }
+            for (int e = 0; e < 2; ++e) grow = grow || fmaxf(S[i][e], S[i][2 + e]) > m_run[i][e] + REF_GAP;
         const int ph = it % 3;   // three flags in turn: the one of the next tile is cleared two barriers after its last reader
         if (__any_sync(0xffffffffu, grow) && lane == 0) flag[ph] = 1;
         if (tid == 0) flag[ph == 2 ? 0 : ph + 1] = 0;
+        refill_if_last(last_k, 2 * it, sk_now);
         // P and the V scales of this tile replace those of the previous tile: every warp must be done with its P V
         if (it > 0) {
             int spins = 0;
@@ -410,6 +411,18 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
         }
         __syncthreads();   // P, the V scales, the warps' maxima and the flag are visible
         if (flag[ph]) {
+            // the warps' row maxima over their 16 keys, exchanged through shared memory
+#pragma unroll
+            for (int i = 0; i < NT; ++i)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    float mx = fmaxf(S[i][e], S[i][2 + e]);
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+                    if (g == 0) wmax[w * NT * 8 + 8 * i + 2 * t + e] = mx;
+                }
+            __syncthreads();
             float fsc[NT][2];
 #pragma unroll
             for (int i = 0; i < NT; ++i)
@@ -509,7 +522,8 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
                 }
             }
         }
-        consumed(1, 2 * it + 1, sv_now);
+        last_v = arrive(1);
+        sv_prev = sv_now;
     }
 
     // ---------------- write the unit's partial ----------------
