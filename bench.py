@@ -40,7 +40,7 @@ HEAD_BYTES = {1: 512, 2: 144, 8: 272}
 
 # DRAM traffic figures taken from the ncu captures summarised under profiles/ (static: a profiler never runs inside a timed
 # bench).  Decode: traffic per algorithmic KV byte on the verify8 capture; it grows in proportion to the keys of a launch.
-DRAM_PER_ALGORITHMIC_BYTE = 405.3 / 362.5
+DRAM_PER_ALGORITHMIC_BYTE = 408.5 / 362.5
 PREFILL8K_DRAM_BYTES = 640.1e6
 
 WORKLOADS = {
@@ -427,7 +427,7 @@ def run_b200(args):
                  "roofline": {"bound": "hbm", "kernel": "decode_part_k (+ merge) per layer call", "achieved": achieved,
                               "peak": peak, "peak_source": "measured" if peaks else "fallback", "unit": "GB/s",
                               "frac": achieved / peak, "traffic": int(DRAM_PER_ALGORITHMIC_BYTE * wl.kv_bytes_layer),
-                              "traffic_source": "dram read + write of one ncu capture of decode_part_k on verify8 (405.3 MB for 362.5 MB "
+                              "traffic_source": "dram read + write of one ncu capture of decode_part_k on verify8 (408.5 MB for 362.5 MB "
                                                 "of KV rows), scaled by the KV bytes of this launch",
                               "avg_launch_ms": att_ms_avg, "algorithmic_bytes_per_launch": int(wl.kv_bytes_layer)}})
     if not args.no_cpu_baseline:
