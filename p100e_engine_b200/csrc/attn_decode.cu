@@ -14,7 +14,7 @@
 //             maximum by 2^7: a tile whose scores stay under it needs one block barrier (P to shared memory as f16, then
 //             P V); only a tile that outgrows it makes the warps exchange maxima, redo P and rescale O.
 //   PV        warp w owns output dims 64w..64w+63: V^T tiles on M, rows on N, fp32 accumulators in registers.
-//   partials  each unit writes unnormalised (O, m, l); a merge kernel combines a row's chunks in chunk order, applies
+//   partials  each unit writes unnormalised (O, m, l); a merge kernel combines a row's chunks in a fixed order, applies
 //             the optional sigmoid gate and normalises (reference formula: dec2_combine_k, src/fast/attn_dec2.cu:430-450).
 // The chunk grid is fixed by absolute key index, and a chunk's arithmetic never depends on the other rows of the call:
 // a row's result is a function of its own keys and of chunk_keys only (row t of a T-row call == the 1-row call).
@@ -580,11 +580,17 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
         }
 }
 
-// Merge a row's chunk partials in chunk order.  grid (rows, Hq), 64 threads (one float4 of the head each).
+// Merge a row's chunk partials.  grid (rows, Hq), 256 threads = 4 groups of 64 (one float4 of the head each): group w sums the
+// chunks w, w + 4, .. in ascending order, the four group sums are added in group order: a fixed order for a given number of
+// chunks, so a row's result does not depend on the rest of the call.
 //   out != nullptr : out = num / den (* sigmoid(gate)); rows that saw no key give zeros
 //   fo  != nullptr : unnormalised num, max in natural-log units, den (for a cross-GPU merge)
-__global__ void __launch_bounds__(64) decode_merge_k(const dec_args a, const float * __restrict__ gate, float * __restrict__ out,
+constexpr int MERGE_GROUPS = 4;
+__global__ void __launch_bounds__(64 * MERGE_GROUPS) decode_merge_k(const dec_args a, const float * __restrict__ gate, float * __restrict__ out,
                                                      float * __restrict__ fo, float * __restrict__ fm, float * __restrict__ fl) {
+    __shared__ float4 gnum[MERGE_GROUPS - 1][64];
+    __shared__ float gden[MERGE_GROUPS - 1];
+    const int lane4 = threadIdx.x & 63, grp = threadIdx.x >> 6;
     const int h = blockIdx.y, row = blockIdx.x, slot = row / a.q_len, j = row - slot * a.q_len;
     const int hk = h / GQA, hh = h - hk * GQA, r = j * GQA + hh, R = a.q_len * GQA;
     const int pos = row_pos(a, slot, j);
@@ -595,19 +601,31 @@ __global__ void __launch_bounds__(64) decode_merge_k(const dec_args a, const flo
     float den = 0.0f;
     float4 num = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll 4
-    for (int c = 0; c < nch; ++c) {   // no early continue: the loads of several chunks are in flight together
+    for (int c = grp; c < nch; c += MERGE_GROUPS) {   // no early continue: the loads of several chunks are in flight together
         const float ms = a.pm[(unit0 + c) * R + r];
         const float f = ms == B200_NEG_INF ? 0.0f : ex2f(ms - M);   // a chunk the row did not see holds zeros: adds nothing
         den = fmaf(f, a.pl[(unit0 + c) * R + r], den);
-        const float4 o = reinterpret_cast<const float4 *>(a.po + ((unit0 + c) * R + r) * DH)[threadIdx.x];
+        const float4 o = reinterpret_cast<const float4 *>(a.po + ((unit0 + c) * R + r) * DH)[lane4];
         num.x = fmaf(f, o.x, num.x); num.y = fmaf(f, o.y, num.y); num.z = fmaf(f, o.z, num.z); num.w = fmaf(f, o.w, num.w);
     }
-    const size_t oi = ((size_t) row * a.Hq + h) * (DH / 4) + threadIdx.x;
+    if (grp > 0) {
+        gnum[grp - 1][lane4] = num;
+        if (lane4 == 0) gden[grp - 1] = den;
+    }
+    __syncthreads();
+    if (grp > 0) return;
+#pragma unroll
+    for (int w = 0; w < MERGE_GROUPS - 1; ++w) {
+        const float4 o = gnum[w][lane4];
+        num.x += o.x; num.y += o.y; num.z += o.z; num.w += o.w;
+        den += gden[w];
+    }
+    const size_t oi = ((size_t) row * a.Hq + h) * (DH / 4) + lane4;
     if (fo) {   // public partials are plain sums: take the internal 2^PSHIFT out (exact)
         constexpr float U = 1.0f / 256.0f;
         static_assert(PSHIFT == 8.0f, "U must be 2^-PSHIFT");
         reinterpret_cast<float4 *>(fo)[oi] = make_float4(num.x * U, num.y * U, num.z * U, num.w * U);
-        if (threadIdx.x == 0) { fm[(size_t) row * a.Hq + h] = M * LN2; fl[(size_t) row * a.Hq + h] = den * U; }
+        if (lane4 == 0) { fm[(size_t) row * a.Hq + h] = M * LN2; fl[(size_t) row * a.Hq + h] = den * U; }
     }
     if (out) {
         float4 y = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
@@ -862,7 +880,7 @@ int decode_impl(const float * q, const b200_kv_cache * c, float * out, const flo
     else if (c->type == B200_KV_Q8_0) rc = launch_part_nt<B200_KV_Q8_0>(a, grid, s);
     else rc = launch_part_nt<B200_KV_Q4_0>(a, grid, s);
     if (rc != B200_OK) return rc;
-    decode_merge_k<<<dim3(n_slots * q_len, Hq), 64, 0, s>>>(a, gate, out, fo, fm, fl);
+    decode_merge_k<<<dim3(n_slots * q_len, Hq), 64 * MERGE_GROUPS, 0, s>>>(a, gate, out, fo, fm, fl);
     count_launch(2);
     return launch_status(who);
 }
@@ -938,7 +956,7 @@ int decode_noalloc_impl(const float * q, const b200_kv_cache * c, float * out, c
     else if (c->type == B200_KV_Q8_0) rc = launch_part_nt<B200_KV_Q8_0>(a, grid, s);
     else rc = launch_part_nt<B200_KV_Q4_0>(a, grid, s);
     if (rc != B200_OK) return rc;
-    decode_merge_k<<<dim3(n_slots * q_len, Hq), 64, 0, s>>>(a, gate, out, nullptr, nullptr, nullptr);
+    decode_merge_k<<<dim3(n_slots * q_len, Hq), 64 * MERGE_GROUPS, 0, s>>>(a, gate, out, nullptr, nullptr, nullptr);
     count_launch(2);
     return launch_status(who);
 }
