@@ -8,6 +8,7 @@ Workloads (synthetic, seeded; shapes of the configurations the baseline names):
               permutation (default; the configuration the 1/2/4/8-GPU scaling is defined on)
   verify8     8 slots x q_len 4, contexts ~U{1024..32768}, one layer
   long_q4     16 slots x q_len 1, context 131072 each, q4_0, one layer
+  long_q8     the same with a q8_0 cache (plain decode: one query row per slot)
   decode1     1 slot x q_len 1, context 4096, one layer (latency-bound)
   prefill8k   one sequence, 8192 new tokens, no prior context: bf16 Q/K/V -> partial RoPE + quantise + append (q8_0
               pages), tensor-core causal attention over the quantised cache, sigmoid gate; metric = attention
@@ -48,6 +49,7 @@ WORKLOADS = {
     "whole_box": (64, 4, 512, 65536, 16, "q8_0"),
     "verify8": (8, 4, 1024, 32768, 1, "q8_0"),
     "long_q4": (16, 1, 131072, 131072, 1, "q4_0"),
+    "long_q8": (16, 1, 131072, 131072, 1, "q8_0"),
     "decode1": (1, 1, 4096, 4096, 1, "q8_0"),
     # chunked causal prefill: one sequence, T new tokens, p0 = 0 (slots, q_len unused; ctx = T)
     "prefill8k": (1, 0, 8192, 8192, 1, "q8_0"),

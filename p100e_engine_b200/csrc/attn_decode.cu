@@ -40,6 +40,8 @@ constexpr int HDR = 1024;             // shared-memory header: barriers, counter
 #define DEC_CTAS 4
 #endif
 constexpr int CTAS_Q = DEC_CTAS;      // CTAs per SM the quantised kernels are compiled for (register budget 65536 / (128 * CTAS_Q))
+// fewer query rows need fewer accumulator registers: one row tile (q_len 1) runs six CTAs per SM, two run five
+template <uint32_t KT, int NT> constexpr int ctas_per_sm() { return KT == B200_KV_F16 ? 2 : NT == 1 ? CTAS_Q + 2 : NT == 2 ? CTAS_Q + 1 : CTAS_Q; }
 constexpr int QSTR = 576;             // bytes per Q row in shared memory (256 f16 + 64: rows g, g+1 on different bank halves)
 constexpr int PSTR = 144;             // bytes per P row (64 f16 + 16)
 constexpr int SDSTR = 132;            // bytes per V-scale row (64 f16 + 4)
@@ -119,7 +121,7 @@ __device__ __forceinline__ void tma_box4(void * dst, const CUtensorMap * map, in
 }
 
 template <uint32_t KT, int NT>
-__global__ void __launch_bounds__(NTHR, KT == B200_KV_F16 ? 2 : CTAS_Q)
+__global__ void __launch_bounds__(NTHR, ctas_per_sm<KT, NT>())
 decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV) {
     using TR = traits<KT>;
     constexpr int HB = TR::HB, SROW = TR::SROW;
@@ -804,7 +806,7 @@ int launch_part(const dec_args & a_in, dim3 grid, cudaStream_t s) {
     // as many CTAs per SM as the kernel is compiled for, if a ring of two half-tile slots fits that often into the 227 KB of
     // an SM; then the deepest ring (up to 8 slots) that still fits
     auto fits = [](int n, int ctas) { return (size_t) ctas * (smem_bytes<KT, NT>(n) + 1024) <= (size_t) 227 * 1024; };
-    int ctas = KT == B200_KV_F16 ? 2 : CTAS_Q;
+    int ctas = ctas_per_sm<KT, NT>();
     while (ctas > 1 && !fits(2, ctas)) --ctas;
     int nslot = 2;
     while (nslot < 8 && fits(nslot + 1, ctas)) ++nslot;
