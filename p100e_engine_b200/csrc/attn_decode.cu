@@ -1,11 +1,12 @@
 // Split-KV decode / MTP-verify attention over the paged f16 / q8_0 / q4_0 cache, sm_100a.
 //
-// Work unit = (slot, kv head, key chunk): one CTA of 4 warps walks its chunk in 64-key tiles, four CTAs per SM.
+// Work unit = (slot, kv head, key chunk): one CTA of 4 warps walks its chunk in 64-key tiles; four CTAs per SM for three row
+// tiles (q_len 3..4), five for two, six for one (q_len 1), two for f16 caches.
 //   staging   the K rows and the V rows of a tile (one kv head, 64 positions) are each fetched by ONE tiled TMA copy through a
 //             tensor map of the cache (x = row bytes, y = position in page, z = page) into a ring of half-tile slots,
 //             completion counted on mbarriers; rows keep their cache format in shared memory.  The warp that is last to
-//             finish with a slot issues its refill.  Ragged last tiles, f16 caches and pages under 64 rows use per-row
-//             bulk copies instead.
+//             finish with a slot issues its refill.  f16 rows go through a rank-4 map with the 128-byte swizzle.  Ragged
+//             last tiles and pages under 64 rows are staged row by row through registers instead.
 //   QK^T      warp w owns keys 16w..16w+15 of the tile: keys on the MMA M axis, the slot's 6 * q_len query rows on N
 //             (all GQA heads and verify rows share one pass over the KV bytes).  int8 / nibbles are widened to f16
 //             exactly in registers (byte permute + one f16x2 subtract), products accumulate in fp32 on the tensor
