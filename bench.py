@@ -67,6 +67,7 @@ def parse():
     ap.add_argument("--layers", type=int, default=0, help="override the workload's layer count")
     ap.add_argument("--chunk", type=int, default=-1, help="keys per split (-1 = chosen from the batch)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--q-len", type=int, default=0, help="override the workload's query rows per slot (1..4)")
     ap.add_argument("--seed", type=int, default=0xB200)
     return ap.parse_args()
 
@@ -75,7 +76,7 @@ def contexts(args):
     slots, q_len, lo, hi, layers, kv = WORKLOADS[args.workload]
     rng = np.random.default_rng(args.seed)
     n = rng.integers(lo, hi + 1, size=slots).astype(np.int64) if hi > lo else np.full(slots, lo, np.int64)
-    return slots, q_len, n, (args.layers or layers), KV_TYPES[args.kv or kv]
+    return slots, (args.q_len or q_len), n, (args.layers or layers), KV_TYPES[args.kv or kv]
 
 
 # ------------------------------------------------------------------------------------------------ clocks ----
