@@ -126,7 +126,7 @@ def clocks_under_load(index, clocks, run_steps, ms_total, steps):
     """A timed region shorter than nvidia-smi's start-up yields no sample: the same steps are then repeated, untimed, for
     about a second with the sampler running, and those samples are reported (marked as taken on a repeat).  The decision
     and the number of repeats follow from the (rank-reduced) time of the timed region, so every rank does the same."""
-    if ms_total >= 600.0 or clocks.get("reasons") == ["unavailable"]:
+    if ms_total >= 350.0 or clocks.get("reasons") == ["unavailable"]:
         return clocks
     import torch
     reps = min(20000, int(1200.0 / max(ms_total / max(steps, 1), 1e-3)) + 1)
