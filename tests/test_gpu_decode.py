@@ -52,6 +52,27 @@ def test_decode_vs_oracle_depths(cuda, lib, tname):
 
 
 @pytest.mark.parametrize("tname", ["q8_0", "f16", "q4_0"])
+def test_one_kv_head_shard_vs_oracle(cuda, lib, tname):
+    """the shape one GPU of a 4- or 8-GPU run holds: a single kv head (rows of 272 / 512 / 144 bytes), 6 query heads"""
+    import torch
+    from p100e_engine_b200 import fast
+    kt = TYPES[tname]
+    n, hq = 1500, 6
+    c, oc = _filled(kt, n, cuda, seed=31, hkv=1)
+    q = util.rng_normal(33, (4, hq, D))
+    qd = util.to_dev(q, cuda)
+    out = torch.zeros(4, hq, D, device=cuda)
+    for T in (1, 4):
+        for p0 in (0, 63, 64, 700, n - T):
+            out.fill_(float("nan"))
+            assert fast.attn_decode(qd, c, out, T, p0, hq, SCALE)
+            torch.cuda.synchronize()
+            ref = orc.attention(q[:T], oc, T, hq, SCALE, p0=p0)
+            util.check_close(out[:T].cpu().numpy(), ref, "%s one head T=%d p0=%d" % (tname, T, p0))
+    assert fast.device_status() == 0
+
+
+@pytest.mark.parametrize("tname", ["q8_0", "f16", "q4_0"])
 def test_decode_config1_vs_oracle_and_reference(cuda, lib, tname):
     """Single-sequence decode shape: one slot, q_len 1, context 4096, 16 pages of 256 in a seeded permutation, sigmoid gate;
     also against the reference's attn_decode on the same paged cache"""
