@@ -40,6 +40,23 @@ def test_prefill_vs_oracle(cuda, lib, tname, p0, T):
     util.check_close(out.cpu().numpy(), ref, "prefill %s p0=%d T=%d" % (tname, p0, T))
 
 
+@pytest.mark.parametrize("tname", ["q8_0", "f16", "q4_0"])
+def test_prefill_one_kv_head_shard(cuda, lib, tname):
+    """the shape one GPU of a 4-GPU run holds: one kv head, 6 query heads; odd number of 64-key images (a last half step)"""
+    import torch
+    from p100e_engine_b200 import fast
+    kt = TYPES[tname]
+    p0, T, hq = 130, 250, 6
+    c, oc = _filled(kt, p0 + T, cuda, 55, hkv=1)
+    q = util.rng_normal(56, (T, hq, D))
+    out = torch.full((T, hq, D), float("nan"), device=cuda)
+    assert fast.attn_prefill(util.to_dev(q, cuda), c, out, T, p0, hq, SCALE)
+    torch.cuda.synchronize()
+    assert fast.device_status() == 0
+    ref = orc.attention(q, oc, T, hq, SCALE, p0=p0)
+    util.check_close(out.cpu().numpy(), ref, "prefill one head %s" % tname)
+
+
 @pytest.mark.parametrize("tname", ["q8_0", "q4_0"])
 def test_prefill_gated_paged_vs_oracle_and_reference(cuda, lib, tname):
     """paged cache (seeded permutation), caller scratch, fused gate; against the oracle and the reference's fp32
