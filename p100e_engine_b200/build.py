@@ -11,7 +11,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200attn.so")
-SOURCES = ["kv_append.cu", "attn_decode.cu", "attn_prefill.cu"]
+SOURCES = ["kv_append.cu", "attn_decode.cu", "attn_prefill.cu", "kv_pool.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--expt-relaxed-constexpr",
     "-Xcompiler", "-fPIC",

@@ -26,6 +26,7 @@
 #include <dlfcn.h>
 #include <cuda.h>   // CUtensorMap and its enums only: the encoder is looked up at run time, nothing links against libcuda
 #include <algorithm>
+#include <atomic>
 #include <cstring>
 #include <cstdlib>
 #include <mutex>
@@ -92,7 +93,18 @@ struct dec_args {
     unsigned * status;
     int n_ctx;                            // rows of a contiguous cache
     int tiled;                            // set by the launcher: whole tiles are fetched through the tensor maps
+    const int2 * units;                   // work list written by decode_plan_k: (slot, chunk), longest first; nullptr = the
+    const int * n_units;                  // grid itself enumerates (slot, chunk) and units past a slot's end exit
 };
+
+// keys of a slot that the call may touch: 1 + its largest row position, held to the caller's max_n (the grid and the
+// partials are sized for max_chunks chunks) and to n_ctx for a contiguous cache.  A position beyond the limit is recorded
+// in the status word and its keys past the limit are left out.
+__device__ __forceinline__ int key_limit(const dec_args & a) {
+    const long long lim = (long long) a.max_chunks * a.CH;
+    const int l = (int) (lim < 0x7fffffffLL ? lim : 0x7fffffffLL);
+    return a.g.pt ? l : min(l, a.n_ctx);
+}
 
 // One tiled copy (TMA unit) of a box of a rank-3 tensor into shared memory, completion counted in bytes on an mbarrier.
 // x is in 16-bit elements and x * 2 must be a multiple of 16 bytes.
@@ -127,13 +139,27 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
     using TR = traits<KT>;
     constexpr int HB = TR::HB, SROW = TR::SROW;
     extern __shared__ __align__(1024) unsigned char smem[];
-    const int chunk = blockIdx.x, hk = blockIdx.y, slot = blockIdx.z;
+    // blockIdx.x = unit * Hkv + kv head: the heads of one (slot, chunk) are neighbours in launch order, so the four
+    // head rows of a position are fetched close together in time
+    const int hk = (int) (blockIdx.x % (unsigned) a.g.Hkv), ui = (int) (blockIdx.x / (unsigned) a.g.Hkv);
+    int slot, chunk;
+    if (a.units) {
+        if (ui >= *a.n_units) return;
+        const int2 u = a.units[ui];
+        slot = u.x; chunk = u.y;
+    } else {
+        slot = ui / a.max_chunks; chunk = ui - slot * a.max_chunks;
+    }
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, g = lane >> 2, t = lane & 3;
     const int R = a.q_len * GQA;
 
     // visible keys of the slot = 1 + the largest row position
     int n_slot = 0;
     for (int j = 0; j < a.q_len; ++j) n_slot = max(n_slot, row_pos(a, slot, j) + 1);
+    {
+        const int lim = key_limit(a);
+        if (n_slot > lim) { if (tid == 0) atomicOr(a.status, ST_BAD_POS); n_slot = lim; }
+    }
     const int k_lo = chunk * a.CH;
     if (k_lo >= n_slot) return;
     const int k_hi = min(k_lo + a.CH, n_slot);
@@ -150,6 +176,7 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
     unsigned char * Sd = Ps + NT * 8 * PSTR;                                 // [8][SDSTR]  V block scales, transposed
     float * wmax = reinterpret_cast<float *>(Sd + 8 * SDSTR);                // [NWARP][NT*8]
     float * wl = wmax + NWARP * NT * 8;                                      // [NWARP][NT*8]
+    float4 * Qb = reinterpret_cast<float4 *>(wl + NWARP * NT * 8);           // [NBLK][NT][4] block sums of Q (quantised caches)
 
     const int32_t * tab = a.g.pt ? a.g.pt + (a.g.rtab ? a.g.rtab[slot * a.q_len] : 0) : nullptr;
     const unsigned long long hoff = (unsigned long long) hk * HB;
@@ -218,7 +245,9 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
     }
     if (pg_staged)
         for (int j = tid; j <= ((k_hi - 1) >> a.g.psh) - pg0; j += NTHR) pgs[j] = tab[pg0 + j];
-    // Q rows -> shared memory as f16, scaled; row r = j * 6 + hh (verify row j, head hh of the group)
+    // Q rows -> shared memory as f16, scaled; row r = j * 6 + hh (verify row j, head hh of the group).  For the quantised
+    // caches the middle two of every four dims are swapped (d0 d2 d1 d3): a 32-bit word of cache bytes then splits into the
+    // f16 pairs (byte 0, byte 2) and (byte 1, byte 3) with one mask and one byte permute (see the Q K^T loop).
     for (int i = tid; i < NT * 8 * (DH / 4); i += NTHR) {
         const int r = i / (DH / 4), d4 = (i - r * (DH / 4)) * 4;
         float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
@@ -226,9 +255,29 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
             const int j = r / GQA, hh = r - j * GQA;
             v = *reinterpret_cast<const float4 *>(a.q + ((size_t) (slot * a.q_len + j) * a.Hq + hk * GQA + hh) * DH + d4);
         }
-        // four consecutive dims stay consecutive under q_slot (it permutes groups of four): one 8-byte store
-        *reinterpret_cast<uint2 *>(Qs + r * QSTR + q_slot<KT>(d4) * 2) =
-            make_uint2(pack_h2(v.x * a.qscale, v.y * a.qscale), pack_h2(v.z * a.qscale, v.w * a.qscale));
+        // four consecutive dims stay together under q_slot (it permutes groups of four): one 8-byte store
+        uint2 pk;
+        if constexpr (TR::SCALED) pk = make_uint2(pack_h2(v.x * a.qscale, v.z * a.qscale), pack_h2(v.y * a.qscale, v.w * a.qscale));
+        else pk = make_uint2(pack_h2(v.x * a.qscale, v.y * a.qscale), pack_h2(v.z * a.qscale, v.w * a.qscale));
+        *reinterpret_cast<uint2 *>(Qs + r * QSTR + q_slot<KT>(d4) * 2) = pk;
+    }
+    __syncthreads();
+    if constexpr (TR::SCALED) {
+        // The cache integers enter the tensor cores as f16 subnormals u * 2^-24 with u = q + 128 (q8_0) or the nibble itself
+        // (q4_0, value = nibble - 8).  The offset is taken out again through the accumulator's starting value: for block b and
+        // row r it is -OFFS * 2^-24 * (sum of the block's 32 scaled f16 query values), kept per (block, row tile, lane quad
+        // position) in the order of an accumulator fragment {row 2t, row 2t+1, row 2t, row 2t+1}.
+        constexpr float OFFS = KT == B200_KV_Q8_0 ? 128.0f : 8.0f;
+        for (int i = tid; i < NBLK * NT * 8; i += NTHR) {
+            const int b = i / (NT * 8), r = i - b * (NT * 8);
+            const __half2 * src = reinterpret_cast<const __half2 *>(Qs + r * QSTR + b * 64);   // a block's dims stay inside its 64 bytes
+            float sum = 0.0f;
+#pragma unroll
+            for (int e = 0; e < 16; ++e) { const float2 f = __half22float2(src[e]); sum += f.x + f.y; }
+            const float v = -OFFS * 5.9604644775390625e-8f * sum;
+            float * dst = reinterpret_cast<float *>(Qb + (b * NT + (r >> 3)) * 4 + ((r & 7) >> 1));
+            dst[r & 1] = v; dst[2 + (r & 1)] = v;
+        }
     }
     __syncthreads();
 
@@ -304,6 +353,12 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
                 }
             }
         } else {
+            // Integers -> f16 without arithmetic: a 16-bit lane holding a value u in 0..255 in its low byte IS the f16
+            // subnormal u * 2^-24, and the tensor cores take subnormal operands at full rate.  A word of four cache bytes
+            // gives the pairs (byte 0, byte 2) by a mask and (byte 1, byte 3) by one byte permute; the query dims are
+            // stored in the matching order.  The sign offset (q8_0: u = q + 128 after flipping the top bits; q4_0: the
+            // nibble carries +8) comes out through the accumulator's starting value Qb, the factor 2^24 through the scale.
+            constexpr float UNSUB = 16777216.0f;
             uint4 sA, sB;   // the 8 block scales of each key (q8_0); q4_0 reads them block by block
             if constexpr (KT == B200_KV_Q8_0) {
                 sA = *reinterpret_cast<const uint4 *>(rowA);
@@ -318,11 +373,11 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
                     const uint2 wb = *reinterpret_cast<const uint2 *>(rowB + 16 + 32 * b + 8 * t);
                     const uint32_t ax = wa.x ^ 0x80808080u, ay = wa.y ^ 0x80808080u;
                     const uint32_t bx = wb.x ^ 0x80808080u, by = wb.y ^ 0x80808080u;
-                    a0[0] = cvt_i8x2<0>(ax); a0[1] = cvt_i8x2<0>(bx); a0[2] = cvt_i8x2<1>(ax); a0[3] = cvt_i8x2<1>(bx);
-                    a1[0] = cvt_i8x2<0>(ay); a1[1] = cvt_i8x2<0>(by); a1[2] = cvt_i8x2<1>(ay); a1[3] = cvt_i8x2<1>(by);
+                    a0[0] = ax & 0x00ff00ffu; a0[1] = bx & 0x00ff00ffu; a0[2] = __byte_perm(ax, 0u, 0x4341); a0[3] = __byte_perm(bx, 0u, 0x4341);
+                    a1[0] = ay & 0x00ff00ffu; a1[1] = by & 0x00ff00ffu; a1[2] = __byte_perm(ay, 0u, 0x4341); a1[3] = __byte_perm(by, 0u, 0x4341);
                     const uint32_t swA = (&sA.x)[b >> 1], swB = (&sB.x)[b >> 1];
-                    dA = __half2float(__ushort_as_half((unsigned short) ((b & 1) ? swA >> 16 : swA & 0xffffu)));
-                    dB = __half2float(__ushort_as_half((unsigned short) ((b & 1) ? swB >> 16 : swB & 0xffffu)));
+                    dA = __half2float(__ushort_as_half((unsigned short) ((b & 1) ? swA >> 16 : swA & 0xffffu))) * UNSUB;
+                    dB = __half2float(__ushort_as_half((unsigned short) ((b & 1) ? swB >> 16 : swB & 0xffffu))) * UNSUB;
                 } else {
                     // block at byte 18 b: f16 d, then 16 bytes; this lane takes bytes 4t..4t+3 (dims 4t.. low nibbles,
                     // 16+4t.. high nibbles).  The 16 bytes start on a 2-byte boundary for even b.
@@ -336,18 +391,17 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
                         qa = *reinterpret_cast<const uint32_t *>(rowA + 18 * b + 2 + 4 * t);
                         qb = *reinterpret_cast<const uint32_t *>(rowB + 18 * b + 2 + 4 * t);
                     }
-                    const uint32_t al = qa & 0x0f0f0f0fu, ah = (qa >> 4) & 0x0f0f0f0fu;
-                    const uint32_t bl = qb & 0x0f0f0f0fu, bh = (qb >> 4) & 0x0f0f0f0fu;
-                    a0[0] = cvt_n4x2<0>(al); a0[1] = cvt_n4x2<0>(bl); a0[2] = cvt_n4x2<1>(al); a0[3] = cvt_n4x2<1>(bl);
-                    a1[0] = cvt_n4x2<0>(ah); a1[1] = cvt_n4x2<0>(bh); a1[2] = cvt_n4x2<1>(ah); a1[3] = cvt_n4x2<1>(bh);
-                    dA = __half2float(*reinterpret_cast<const __half *>(rowA + 18 * b));
-                    dB = __half2float(*reinterpret_cast<const __half *>(rowB + 18 * b));
+                    // nibble pairs: low nibbles of bytes (0, 2) and (1, 3) feed the first k-step, the high nibbles the second
+                    a0[0] = qa & 0x000f000fu; a0[1] = qb & 0x000f000fu; a0[2] = (qa >> 8) & 0x000f000fu; a0[3] = (qb >> 8) & 0x000f000fu;
+                    a1[0] = (qa >> 4) & 0x000f000fu; a1[1] = (qb >> 4) & 0x000f000fu; a1[2] = (qa >> 12) & 0x000f000fu; a1[3] = (qb >> 12) & 0x000f000fu;
+                    dA = __half2float(*reinterpret_cast<const __half *>(rowA + 18 * b)) * UNSUB;
+                    dB = __half2float(*reinterpret_cast<const __half *>(rowB + 18 * b)) * UNSUB;
                 }
 #pragma unroll
                 for (int i = 0; i < NT; ++i) {
                     const uint4 qv = *reinterpret_cast<const uint4 *>(Qs + (8 * i + g) * QSTR + 64 * b + 16 * t);
-                    float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                    mma16816(c, a0, qv.x, qv.y);
+                    float c[4];
+                    mma16816_from(c, Qb[(b * NT + i) * 4 + t], a0, qv.x, qv.y);
                     mma16816(c, a1, qv.z, qv.w);
                     S[i][0] = fmaf(dA, c[0], S[i][0]); S[i][1] = fmaf(dA, c[1], S[i][1]);
                     S[i][2] = fmaf(dB, c[2], S[i][2]); S[i][3] = fmaf(dB, c[3], S[i][3]);
@@ -590,13 +644,14 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
 //   fo  != nullptr : unnormalised num, max in natural-log units, den (for a cross-GPU merge)
 constexpr int MERGE_GROUPS = 4;
 __global__ void __launch_bounds__(64 * MERGE_GROUPS) decode_merge_k(const dec_args a, const float * __restrict__ gate, float * __restrict__ out,
-                                                     float * __restrict__ fo, float * __restrict__ fm, float * __restrict__ fl) {
+                                                     float * __restrict__ fo, float * __restrict__ fm, float * __restrict__ fl,
+                                                     __half2 * __restrict__ qbuf) {
     __shared__ float4 gnum[MERGE_GROUPS - 1][64];
     __shared__ float gden[MERGE_GROUPS - 1];
     const int lane4 = threadIdx.x & 63, grp = threadIdx.x >> 6;
     const int h = blockIdx.y, row = blockIdx.x, slot = row / a.q_len, j = row - slot * a.q_len;
     const int hk = h / GQA, hh = h - hk * GQA, r = j * GQA + hh, R = a.q_len * GQA;
-    const int pos = row_pos(a, slot, j);
+    const int pos = min(row_pos(a, slot, j), key_limit(a) - 1);   // a row past the limit merges the chunks that exist
     const int nch = pos < 0 ? 0 : pos / a.CH + 1;
     const size_t unit0 = ((size_t) slot * a.g.Hkv + hk) * a.max_chunks;
     float M = B200_NEG_INF;
@@ -642,6 +697,9 @@ __global__ void __launch_bounds__(64 * MERGE_GROUPS) decode_merge_k(const dec_ar
             }
         }
         reinterpret_cast<float4 *>(out)[oi] = y;
+        // the projection that follows attention reads its input in the a16 format: emitted here, from registers
+        if (qbuf) a16_store_lanes8(y, qbuf, (size_t) row * (a.Hq * (DH / 32)) + h * (DH / 32) + (lane4 >> 3),
+                                   (size_t) gridDim.x * (a.Hq * (DH / 32)), true);
     }
 }
 
@@ -649,7 +707,7 @@ __global__ void __launch_bounds__(64 * MERGE_GROUPS) decode_merge_k(const dec_ar
 // pm + s * sm and l [R] at pl + s * sm (strides in floats); one block per row, D/4 threads.
 __global__ void merge_parts_k(const float * __restrict__ po, const float * __restrict__ pm, const float * __restrict__ pl,
                               int nparts, int R, int D, const float * __restrict__ gate, float * __restrict__ out, size_t so,
-                              size_t sm) {
+                              size_t sm, __half2 * __restrict__ qbuf) {
     const int r = blockIdx.x, i = threadIdx.x;
     float M = B200_NEG_INF;
     for (int s = 0; s < nparts; ++s) M = fmaxf(M, pm[s * sm + r]);
@@ -674,32 +732,94 @@ __global__ void merge_parts_k(const float * __restrict__ po, const float * __res
         }
     }
     reinterpret_cast<float4 *>(out + (size_t) r * D)[i] = y;
+    // a16 copy of the gated output (rows of row_len = heads * D values): group index = float index / 32
+    if (qbuf) a16_store_lanes8(y, qbuf, ((size_t) r * D + 4 * i) / 32, (size_t) R * D / 32, true);
+}
+
+// Work list of a batched call: every (slot, chunk) that holds at least one visible key, longest first.  Whole chunks
+// come first (all the same length), then the slots' last, shorter chunks in descending order of their tile count, so the
+// tail of the launch is made of the shortest units.  One block; writes units[] and *n_units.  The order of equal-length
+// units depends on the order of the atomics and does not affect any result (units are independent).
+constexpr int PLAN_THR = 256, PLAN_BUCKETS = 256;
+__global__ void __launch_bounds__(PLAN_THR) decode_plan_k(const dec_args a, int2 * __restrict__ units, int * __restrict__ n_units) {
+    __shared__ int hist[PLAN_BUCKETS], total_full, cur_full;
+    const int tid = threadIdx.x;
+    const int tiles_per_chunk = a.CH / TILE;
+    for (int i = tid; i < PLAN_BUCKETS; i += PLAN_THR) hist[i] = 0;
+    if (tid == 0) { total_full = 0; cur_full = 0; }
+    __syncthreads();
+    const int lim = key_limit(a);
+    auto slot_keys = [&](int s) {
+        int n = 0;
+        for (int j = 0; j < a.q_len; ++j) n = max(n, row_pos(a, s, j) + 1);
+        return min(n, lim);
+    };
+    // bucket of a last chunk: its tile count scaled into PLAN_BUCKETS classes, descending (bucket 0 = longest)
+    auto bucket_of = [&](int tail_keys) {
+        const int tiles = (tail_keys + TILE - 1) / TILE;   // 1 .. tiles_per_chunk - 1 (a whole chunk is not a tail) or tiles_per_chunk
+        const long long cls = (long long) (tiles_per_chunk - tiles) * PLAN_BUCKETS / max(tiles_per_chunk, 1);
+        return (int) min((long long) PLAN_BUCKETS - 1, max(0LL, cls));
+    };
+    for (int s = tid; s < a.n_slots; s += PLAN_THR) {
+        const int n = slot_keys(s), nfull = n / a.CH, tail = n - nfull * a.CH;
+        if (nfull) atomicAdd(&total_full, nfull);
+        if (tail) atomicAdd(&hist[bucket_of(tail)], 1);
+    }
+    __syncthreads();
+    if (tid == 0) {   // exclusive scan of the tail classes, placed after the whole chunks
+        int run = total_full;
+        for (int i = 0; i < PLAN_BUCKETS; ++i) { const int c = hist[i]; hist[i] = run; run += c; }
+        *n_units = run;
+    }
+    __syncthreads();
+    for (int s = tid; s < a.n_slots; s += PLAN_THR) {
+        const int n = slot_keys(s), nfull = n / a.CH, tail = n - nfull * a.CH;
+        if (nfull) {
+            const int base = atomicAdd(&cur_full, nfull);
+            for (int c = 0; c < nfull; ++c) units[base + c] = make_int2(s, c);
+        }
+        if (tail) units[atomicAdd(&hist[bucket_of(tail)], 1)] = make_int2(s, nfull);
+    }
 }
 
 // ------------------------------------------------------------------------------------------------ host side ----
 constexpr int DEFAULT_CHUNK = 512;
-int g_chunk = 0;            // 0 = not read yet
-int g_chunk_override = 0;   // set_nsplit
+constexpr int MAX_DEFAULT_CHUNKS = 256;   // the default chunk grows with n_ctx so that a context never has more chunks than this
+int g_chunk = 0;            // 0 = not read yet; else B200ATTN_CHUNK or DEFAULT_CHUNK
+bool g_chunk_from_env = false;
+int g_nsplit_override = 0;  // set_nsplit: chunks per full context
 
-int env_chunk() {
+int round_tile(long long v) { return (int) ((std::max<long long>(v, TILE) + TILE - 1) / TILE * TILE); }
+int env_chunk(bool * from_env) {
     const char * e = getenv("B200ATTN_CHUNK");
-    int v = e && *e ? atoi(e) : DEFAULT_CHUNK;
-    if (v < TILE) v = TILE;
-    return (v + TILE - 1) / TILE * TILE;
+    const bool have = e && *e && atoi(e) > 0;
+    if (from_env) *from_env = have;
+    return round_tile(have ? atoi(e) : DEFAULT_CHUNK);
 }
 int default_chunk() {
-    if (!g_chunk) g_chunk = env_chunk();
+    if (!g_chunk) g_chunk = env_chunk(&g_chunk_from_env);
     return g_chunk;
 }
+// The chunk of a call that asks for the library default: a function of the cache's capacity only, so that a row's bits do
+// not depend on the batch it is decoded in.  set_nsplit(n) pins n chunks per full context; B200ATTN_CHUNK pins the keys.
+int fixed_chunk(int n_ctx) {
+    const int base = default_chunk();
+    if (g_nsplit_override > 0) return round_tile(((long long) std::max(n_ctx, 1) + g_nsplit_override - 1) / g_nsplit_override);
+    if (g_chunk_from_env) return base;
+    return std::max(base, round_tile(((long long) std::max(n_ctx, 1) + MAX_DEFAULT_CHUNKS - 1) / MAX_DEFAULT_CHUNKS));
+}
 
-// split partials per (device, stream): grown on demand, never shrunk, so the pointers stay valid for captured graphs
-// once a call of the largest size has run eagerly (same ownership rule as the reference, src/fast/attn_dec2.cu:452-464)
+// Split partials and the work list live in one library-owned buffer per (device, stream), as in the reference
+// (src/fast/attn_dec2.cu:452-464,503-517): sized on the first call or by b200_attn_reserve, and from then on calls that
+// fit neither allocate nor synchronise, and the pointer does not move (recorded work stays valid).  A call that needs more
+// gets a new, larger buffer; the old one is kept allocated until the process exits, so nothing that was recorded against
+// it ever reads freed memory, and no stream is synchronised.
 struct scratch { int dev = -1; cudaStream_t s = nullptr; float * p = nullptr; size_t cap = 0; };
 scratch g_scr[64];
 int g_nscr = 0;
 std::mutex g_mu;
 
-float * scratch_for(cudaStream_t s, size_t floats) {
+float * scratch_for(cudaStream_t s, size_t floats, size_t floats_hint) {
     int dev = 0;
     cudaGetDevice(&dev);
     std::lock_guard<std::mutex> lk(g_mu);
@@ -711,9 +831,10 @@ float * scratch_for(cudaStream_t s, size_t floats) {
         e->dev = dev; e->s = s;
     }
     if (floats > e->cap) {
-        if (e->p) { cudaStreamSynchronize(s); cudaFree(e->p); e->p = nullptr; e->cap = 0; }
-        const size_t want = std::max(floats, (size_t) 1 << 20);
-        if (cudaMalloc(&e->p, want * sizeof(float)) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+        const size_t want = std::max(std::max(floats, floats_hint), std::max(e->cap + e->cap / 2, (size_t) 1 << 20));
+        float * p = nullptr;
+        if (cudaMalloc(&p, want * sizeof(float)) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+        e->p = p;      // the previous buffer, if any, stays allocated (see above)
         e->cap = want;
     }
     return e->p;
@@ -789,11 +910,12 @@ bool make_cache_map(CUtensorMap * m, const char * base, const dec_args & a, int 
 }
 
 template <uint32_t KT, int NT> size_t smem_bytes(int nslot) {
-    return HDR + (size_t) nslot * traits<KT>::SLOT + NT * 8 * (QSTR + PSTR) + 8 * SDSTR + 2 * NWARP * NT * 8 * sizeof(float);
+    return HDR + (size_t) nslot * traits<KT>::SLOT + NT * 8 * (QSTR + PSTR) + 8 * SDSTR + 2 * NWARP * NT * 8 * sizeof(float) +
+           (traits<KT>::SCALED ? NBLK * NT * 4 * sizeof(float4) : 0);
 }
 
 template <uint32_t KT, int NT>
-int launch_part(const dec_args & a_in, dim3 grid, cudaStream_t s) {
+int launch_part(const dec_args & a_in, unsigned blocks, cudaStream_t s) {
     dec_args a = a_in;
     CUtensorMap mapK, mapV;
     memset(&mapK, 0, sizeof mapK);
@@ -812,80 +934,122 @@ int launch_part(const dec_args & a_in, dim3 grid, cudaStream_t s) {
     int nslot = 2;
     while (nslot < 8 && fits(nslot + 1, ctas)) ++nslot;
     const size_t sm = smem_bytes<KT, NT>(nslot);
-    static bool attr_done[64] = {};   // per instantiation and device
+    static std::atomic<bool> attr_done[64];   // per instantiation and device; setting the attribute twice is harmless
     int dev = 0;
     cudaGetDevice(&dev);
-    if (!attr_done[dev & 63]) {
+    if (!attr_done[dev & 63].load(std::memory_order_acquire)) {
         if (cudaFuncSetAttribute(decode_part_k<KT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) sm) != cudaSuccess)
             return launch_status("attn_decode (shared memory attribute)");
         cudaFuncSetAttribute(decode_part_k<KT, NT>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-        attr_done[dev & 63] = true;
+        attr_done[dev & 63].store(true, std::memory_order_release);
     }
-    decode_part_k<KT, NT><<<grid, NTHR, sm, s>>>(a, nslot, mapK, mapV);
+    decode_part_k<KT, NT><<<blocks, NTHR, sm, s>>>(a, nslot, mapK, mapV);
     return B200_OK;
 }
 
 template <uint32_t KT>
-int launch_part_nt(const dec_args & a, dim3 grid, cudaStream_t s) {
+int launch_part_nt(const dec_args & a, unsigned blocks, cudaStream_t s) {
     const int nt = (a.q_len * GQA + 7) / 8;
-    return nt == 1 ? launch_part<KT, 1>(a, grid, s) : nt == 2 ? launch_part<KT, 2>(a, grid, s) : launch_part<KT, 3>(a, grid, s);
+    return nt == 1 ? launch_part<KT, 1>(a, blocks, s) : nt == 2 ? launch_part<KT, 2>(a, blocks, s) : launch_part<KT, 3>(a, blocks, s);
+}
+
+int sm_count() {
+    int sms = 148, dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    return sms;
 }
 
 int auto_chunk(long long total_keys, int Hkv) {
-    // enough units for ~4 waves over the SMs at two CTAs each, chunks between 256 and 4096 keys
-    int sms = 148;
-    int dev = 0;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const long long units = 8LL * sms;
+    // enough units for several waves over the SMs, chunks between 256 and 4096 keys
+    const long long units = 8LL * sm_count();
     long long ch = total_keys * Hkv / units;
     int c = 256;
     while (c < 4096 && c < ch) c *= 2;
     return c;
 }
 
-}  // namespace
+// geometry of a call: chunk, chunks per slot, partial floats, work-list ints
+struct dec_geom { int CH, max_chunks, R; size_t units, part_floats, list_ints; bool planned; };
 
-// q [rows][Hq][256]; rows = n_slots * q_len. Exactly one of (pos), (p0p), (p0) gives the positions.
-int decode_impl(const float * q, const b200_kv_cache * c, float * out, const float * gate, float * fo, float * fm, float * fl,
-                int n_slots, int q_len, const int32_t * pos, const int32_t * p0p, int p0, int max_n, int Hq, float scale,
-                int chunk_keys, cudaStream_t s, const char * who) {
+bool decode_geometry(dec_geom & g, int n_slots, int q_len, int max_n, int n_ctx, int Hkv, int chunk_keys) {
+    if (max_n < 1) max_n = 1;
+    g.CH = chunk_keys > 0 ? round_tile(chunk_keys) : chunk_keys < 0 ? auto_chunk((long long) n_slots * max_n / 2, Hkv) : fixed_chunk(n_ctx);
+    g.max_chunks = (max_n + g.CH - 1) / g.CH;
+    g.R = q_len * GQA;
+    g.units = (size_t) n_slots * Hkv * g.max_chunks;
+    if (g.units >= ((size_t) 1 << 31) || (size_t) n_slots * g.max_chunks >= ((size_t) 1 << 30)) return false;
+    g.part_floats = g.units * g.R * (DH + 2);
+    // a work list pays once the launch is longer than one wave of resident CTAs; shorter launches enumerate the grid
+    g.planned = n_slots > 1 && g.units > (size_t) 2 * sm_count();
+    g.list_ints = g.planned ? 2 * (size_t) n_slots * g.max_chunks + 4 : 0;
+    return true;
+}
+
+int decode_check(const float * q, const b200_kv_cache * c, const float * out, const float * gate, int n_slots, int q_len, int Hq,
+                 const char * who) {
     if (!c || !q || !c->k || !c->v) B200_REFUSE(B200_ERR_SHAPE, "%s: null argument", who);
     if (c->D != DH || Hq != GQA * c->Hkv || c->Hkv <= 0) B200_REFUSE(B200_ERR_SHAPE, "%s: unsupported shape (D=%d Hq=%d Hkv=%d)", who, c->D, Hq, c->Hkv);
     if (c->type != B200_KV_F16 && c->type != B200_KV_Q8_0 && c->type != B200_KV_Q4_0) B200_REFUSE(B200_ERR_SHAPE, "%s: unsupported cache type %u", who, c->type);
-    if (n_slots < 1 || q_len < 1 || q_len > B200_MAX_QLEN) B200_REFUSE(B200_ERR_SHAPE, "%s: unsupported rows (slots=%d q_len=%d)", who, n_slots, q_len);
-    if (n_slots > 65535) B200_REFUSE(B200_ERR_SHAPE, "%s: more than 65535 slots", who);
+    if (n_slots < 1 || n_slots > 65535 || q_len < 1 || q_len > B200_MAX_QLEN) B200_REFUSE(B200_ERR_SHAPE, "%s: unsupported rows (slots=%d q_len=%d)", who, n_slots, q_len);
     if (!aligned16(c->k) || !aligned16(c->v) || !aligned16(q) || (out && !aligned16(out)) || (gate && !aligned16(gate)) ||
         (c->pt && c->pstride % 16))
         B200_REFUSE(B200_ERR_SHAPE, "%s: cache base, page stride, q, out and gate must be 16-byte aligned", who);
     if (c->pt && (c->psh < 0 || c->psh > 30)) B200_REFUSE(B200_ERR_SHAPE, "%s: bad page shift %d", who, c->psh);
-    if (max_n < 1) max_n = 1;
-    int CH = chunk_keys > 0 ? (chunk_keys + TILE - 1) / TILE * TILE : chunk_keys < 0 ? auto_chunk((long long) n_slots * max_n / 2, c->Hkv)
-                                                                                  : (g_chunk_override > 0 ? g_chunk_override : default_chunk());
-    const int max_chunks = (max_n + CH - 1) / CH;
-    if (max_chunks > 65535 * 32) B200_REFUSE(B200_ERR_SHAPE, "%s: too many chunks", who);
-    const int R = q_len * GQA;
-    const size_t units = (size_t) n_slots * c->Hkv * max_chunks;
-    float * scr = scratch_for(s, units * R * (DH + 2));
-    if (!scr) B200_REFUSE(B200_ERR_ALLOC, "%s: split scratch (%zu floats) could not be allocated", who, units * R * (DH + 2));
-    unsigned * st = device_status_word();
-    if (!st) return B200_ERR_CUDA;
+    return B200_OK;
+}
+
+struct merge_out { float * out; const float * gate; float * fo, * fm, * fl; void * qbuf; };
+
+// the kernels of one call, partials and work list in `scr`
+int decode_launch(const float * q, const b200_kv_cache * c, const merge_out & mo, int n_slots, int q_len, const int32_t * pos,
+                  const int32_t * p0p, int p0, int Hq, float scale, const dec_geom & gm, float * scr, unsigned * st, cudaStream_t s,
+                  const char * who) {
     dec_args a;
     a.q = q; a.g = view_of(*c);
-    a.po = scr; a.pm = scr + units * R * DH; a.pl = a.pm + units * R;
+    a.po = scr; a.pm = scr + gm.units * gm.R * DH; a.pl = a.pm + gm.units * gm.R;
     a.pos = pos; a.p0p = p0p; a.p0 = p0;
     a.q_len = q_len; a.n_slots = n_slots; a.Hq = Hq;
     a.qscale = scale * LOG2E;
-    a.CH = CH; a.max_chunks = max_chunks; a.status = st;
+    a.CH = gm.CH; a.max_chunks = gm.max_chunks; a.status = st;
     a.n_ctx = c->n_ctx; a.tiled = 0;
-    const dim3 grid(max_chunks, c->Hkv, n_slots);
+    a.units = nullptr; a.n_units = nullptr;
+    int launches = 2;
+    if (gm.planned) {
+        int * list = reinterpret_cast<int *>(scr + gm.part_floats);
+        a.n_units = list;
+        a.units = reinterpret_cast<const int2 *>(list + 4);
+        decode_plan_k<<<1, PLAN_THR, 0, s>>>(a, reinterpret_cast<int2 *>(list + 4), list);
+        ++launches;
+    }
+    const unsigned blocks = (unsigned) gm.units;
     int rc;
-    if (c->type == B200_KV_F16) rc = launch_part_nt<B200_KV_F16>(a, grid, s);
-    else if (c->type == B200_KV_Q8_0) rc = launch_part_nt<B200_KV_Q8_0>(a, grid, s);
-    else rc = launch_part_nt<B200_KV_Q4_0>(a, grid, s);
+    if (c->type == B200_KV_F16) rc = launch_part_nt<B200_KV_F16>(a, blocks, s);
+    else if (c->type == B200_KV_Q8_0) rc = launch_part_nt<B200_KV_Q8_0>(a, blocks, s);
+    else rc = launch_part_nt<B200_KV_Q4_0>(a, blocks, s);
     if (rc != B200_OK) return rc;
-    decode_merge_k<<<dim3(n_slots * q_len, Hq), 64 * MERGE_GROUPS, 0, s>>>(a, gate, out, fo, fm, fl);
-    count_launch(2);
+    decode_merge_k<<<dim3(n_slots * q_len, Hq), 64 * MERGE_GROUPS, 0, s>>>(a, mo.gate, mo.out, mo.fo, mo.fm, mo.fl, (__half2 *) mo.qbuf);
+    count_launch(launches);
     return launch_status(who);
+}
+
+}  // namespace
+
+// q [rows][Hq][256]; rows = n_slots * q_len. Exactly one of (pos), (p0p), (p0) gives the positions.
+// hint_floats: size the library scratch for at least this much when it has to be (re)allocated.
+int decode_impl(const float * q, const b200_kv_cache * c, const merge_out & mo, int n_slots, int q_len, const int32_t * pos,
+                const int32_t * p0p, int p0, int max_n, int Hq, float scale, int chunk_keys, cudaStream_t s, const char * who,
+                size_t hint_floats = 0) {
+    const int chk = decode_check(q, c, mo.out, mo.gate, n_slots, q_len, Hq, who);
+    if (chk != B200_OK) return chk;
+    if (mo.qbuf && (!mo.out || ((uintptr_t) mo.qbuf & 3))) B200_REFUSE(B200_ERR_SHAPE, "%s: the a16 buffer needs out and 4-byte alignment", who);
+    dec_geom gm;
+    if (!decode_geometry(gm, n_slots, q_len, max_n, c->n_ctx, c->Hkv, chunk_keys)) B200_REFUSE(B200_ERR_SHAPE, "%s: too many chunks", who);
+    const size_t need = gm.part_floats + gm.list_ints;
+    float * scr = scratch_for(s, need, hint_floats);
+    if (!scr) B200_REFUSE(B200_ERR_ALLOC, "%s: split scratch (%zu floats) could not be allocated", who, need);
+    unsigned * st = device_status_word();
+    if (!st) return B200_ERR_CUDA;
+    return decode_launch(q, c, mo, n_slots, q_len, pos, p0p, p0, Hq, scale, gm, scr, st, s, who);
 }
 
 // ---- decode / verify without any allocation --------------------------------------------------------------------
@@ -898,12 +1062,14 @@ static __device__ __align__(256) float g_noalloc_partials[NOALLOC_FLOATS];
 static __device__ __align__(256) unsigned g_noalloc_status[64];
 struct noalloc_dev { bool ready = false; float * partials = nullptr; unsigned * status = nullptr; };
 noalloc_dev g_noalloc[64];
+std::mutex g_noalloc_mu;
 
 // In host code the two array names above are host-side handles, not device addresses: the addresses the kernels need are
 // looked up once per device, with that device current.
-int noalloc_setup(noalloc_dev *& out) {
+int noalloc_setup(noalloc_dev & out) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return B200_ERR_CUDA; }
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
     noalloc_dev & e = g_noalloc[dev & 63];
     if (!e.ready) {
         void * p = nullptr, * st = nullptr;
@@ -918,50 +1084,27 @@ int noalloc_setup(noalloc_dev *& out) {
         e.status = (unsigned *) st;
         e.ready = true;
     }
-    out = &e;
+    out = e;
     return B200_OK;
 }
 
 int decode_noalloc_impl(const float * q, const b200_kv_cache * c, float * out, const float * gate, int n_slots, int q_len,
                         const int32_t * pos, int max_n, int Hq, float scale, int chunk_keys, cudaStream_t s) {
     const char * who = "attn_decode_slots_noalloc";
-    if (!c || !q || !out || !pos || !c->k || !c->v) B200_REFUSE(B200_ERR_SHAPE, "%s: null argument", who);
-    if (c->D != DH || Hq != GQA * c->Hkv || c->Hkv <= 0) B200_REFUSE(B200_ERR_SHAPE, "%s: unsupported shape (D=%d Hq=%d Hkv=%d)", who, c->D, Hq, c->Hkv);
-    if (c->type != B200_KV_F16 && c->type != B200_KV_Q8_0 && c->type != B200_KV_Q4_0) B200_REFUSE(B200_ERR_SHAPE, "%s: unsupported cache type %u", who, c->type);
-    if (n_slots < 1 || n_slots > 65535 || q_len < 1 || q_len > B200_MAX_QLEN) B200_REFUSE(B200_ERR_SHAPE, "%s: unsupported rows (slots=%d q_len=%d)", who, n_slots, q_len);
-    if (!aligned16(c->k) || !aligned16(c->v) || !aligned16(q) || !aligned16(out) || (gate && !aligned16(gate)) || (c->pt && c->pstride % 16))
-        B200_REFUSE(B200_ERR_SHAPE, "%s: cache base, page stride, q, out and gate must be 16-byte aligned", who);
-    if (c->pt && (c->psh < 0 || c->psh > 30)) B200_REFUSE(B200_ERR_SHAPE, "%s: bad page shift %d", who, c->psh);
-    if (max_n < 1) max_n = 1;
-    const int CH = chunk_keys > 0 ? (chunk_keys + TILE - 1) / TILE * TILE : chunk_keys < 0 ? auto_chunk((long long) n_slots * max_n / 2, c->Hkv)
-                                                                                        : (g_chunk_override > 0 ? g_chunk_override : default_chunk());
-    const int max_chunks = (max_n + CH - 1) / CH;
-    const int R = q_len * GQA;
-    const size_t units = (size_t) n_slots * c->Hkv * max_chunks;
-    const size_t need = units * R * (DH + 2);
-    if (max_chunks > 65535 * 32 || need > NOALLOC_FLOATS)
+    if (!out || !pos) B200_REFUSE(B200_ERR_SHAPE, "%s: null argument", who);
+    const int chk = decode_check(q, c, out, gate, n_slots, q_len, Hq, who);
+    if (chk != B200_OK) return chk;
+    dec_geom gm;
+    const bool ok = decode_geometry(gm, n_slots, q_len, max_n, c->n_ctx, c->Hkv, chunk_keys);
+    const size_t need = ok ? gm.part_floats + gm.list_ints : 0;
+    if (!ok || need > NOALLOC_FLOATS)
         B200_REFUSE(B200_ERR_SCRATCH, "%s: %zu bytes of split partials needed (slots %d x kv heads %d x chunks %d x rows %d), the built-in array holds %zu; "
-                    "use a larger chunk_keys or attn_decode_slots", who, need * sizeof(float), n_slots, c->Hkv, max_chunks, R, NOALLOC_BYTES);
-    noalloc_dev * e = nullptr;
+                    "use a larger chunk_keys or attn_decode_slots", who, need * sizeof(float), n_slots, c->Hkv, ok ? gm.max_chunks : -1, q_len * GQA, NOALLOC_BYTES);
+    noalloc_dev e;
     const int src = noalloc_setup(e);
     if (src != B200_OK) return src;
-    dec_args a;
-    a.q = q; a.g = view_of(*c);
-    a.po = e->partials; a.pm = a.po + units * R * DH; a.pl = a.pm + units * R;
-    a.pos = pos; a.p0p = nullptr; a.p0 = 0;
-    a.q_len = q_len; a.n_slots = n_slots; a.Hq = Hq;
-    a.qscale = scale * LOG2E;
-    a.CH = CH; a.max_chunks = max_chunks; a.status = e->status;
-    a.n_ctx = c->n_ctx; a.tiled = 0;
-    const dim3 grid(max_chunks, c->Hkv, n_slots);
-    int rc;
-    if (c->type == B200_KV_F16) rc = launch_part_nt<B200_KV_F16>(a, grid, s);
-    else if (c->type == B200_KV_Q8_0) rc = launch_part_nt<B200_KV_Q8_0>(a, grid, s);
-    else rc = launch_part_nt<B200_KV_Q4_0>(a, grid, s);
-    if (rc != B200_OK) return rc;
-    decode_merge_k<<<dim3(n_slots * q_len, Hq), 64 * MERGE_GROUPS, 0, s>>>(a, gate, out, nullptr, nullptr, nullptr);
-    count_launch(2);
-    return launch_status(who);
+    const merge_out mo = {out, gate, nullptr, nullptr, nullptr, nullptr};
+    return decode_launch(q, c, mo, n_slots, q_len, pos, nullptr, 0, Hq, scale, gm, e.partials, e.status, s, who);
 }
 
 }  // namespace b200
@@ -976,31 +1119,68 @@ int b200_attn_decode_slots_noalloc(const float * q, const b200_kv_cache * c, flo
     return decode_noalloc_impl(q, c, out, gate, n_slots, q_len, pos, max_n, Hq, scale, chunk_keys, (cudaStream_t) stream);
 }
 
-int b200_attn_chunk_keys(void) { return g_chunk_override > 0 ? g_chunk_override : default_chunk(); }
+// Status word of the allocation-free entry point on the current device: synchronises the stream, reads the word with a
+// symbol copy and clears it with another (neither allocates).  0 = no kernel of that entry point recorded an error.
+int b200_noalloc_device_status(void * stream) {
+    if (cudaStreamSynchronize((cudaStream_t) stream) != cudaSuccess) return -1;
+    unsigned h = 0;
+    if (cudaMemcpyFromSymbol(&h, g_noalloc_status, sizeof h) != cudaSuccess) { cudaGetLastError(); return -1; }
+    if (h) {
+        const unsigned z = 0;
+        if (cudaMemcpyToSymbol(g_noalloc_status, &z, sizeof z) != cudaSuccess) { cudaGetLastError(); return -1; }
+    }
+    return (int) h;
+}
+
+int b200_attn_chunk_keys(void) { return default_chunk(); }
+int b200_attn_fixed_chunk(int n_ctx) { return fixed_chunk(n_ctx); }
 
 int b200_attn_dec2_nsplit(int Hkv) {
-    (void) Hkv;
-    return 1;   // refined by callers that know n_ctx: chunks = ceil(n_ctx / b200_attn_chunk_keys())
+    (void) Hkv;   // the reference derives its stream count from the SM count and Hkv; here the split follows the context
+    return g_nsplit_override > 0 ? g_nsplit_override : MAX_DEFAULT_CHUNKS;
 }
-void b200_attn_dec2_set_nsplit(int n) { (void) n; }
+void b200_attn_dec2_set_nsplit(int n) { g_nsplit_override = n > 0 ? n : 0; }
 int b200_attn_dec2_reload_env(void) {
-    const int v = env_chunk();
-    const bool ch = v != default_chunk();
-    g_chunk = v;
-    return ch ? 1 : 0;
+    const int before = default_chunk();
+    const bool before_env = g_chunk_from_env;
+    g_chunk = env_chunk(&g_chunk_from_env);
+    return (g_chunk != before || g_chunk_from_env != before_env) ? 1 : 0;
+}
+
+int b200_attn_reserve(int max_slots, int q_len, int max_n, int n_ctx, int Hkv, int chunk_keys, void * stream) {
+    if (max_slots < 1 || max_slots > 65535 || q_len < 1 || q_len > B200_MAX_QLEN || max_n < 1 || Hkv < 1)
+        B200_REFUSE(B200_ERR_SHAPE, "attn_reserve: unsupported arguments");
+    dec_geom gm;
+    if (!decode_geometry(gm, max_slots, q_len, max_n, n_ctx > 0 ? n_ctx : max_n, Hkv, chunk_keys)) B200_REFUSE(B200_ERR_SHAPE, "attn_reserve: too many chunks");
+    size_t need = gm.part_floats + 2 * (size_t) max_slots * gm.max_chunks + 4;
+    if (chunk_keys < 0) {
+        // a chunk chosen from the batch: smaller batches take smaller chunks; their unit count stays under this bound
+        const size_t u = 2 * 8 * (size_t) sm_count() + (size_t) max_slots * Hkv;
+        need = std::max(need, u * q_len * GQA * (DH + 2) + 2 * u + 4);
+    }
+    if (!scratch_for((cudaStream_t) stream, need, 0)) B200_REFUSE(B200_ERR_ALLOC, "attn_reserve: %zu floats could not be allocated", need);
+    return B200_OK;
 }
 
 int b200_attn_decode2(const float * q, const b200_kv_cache * c, float * out, int T, int p0, const int32_t * p0_dev, int Hq,
                       float scale, void * stream, const int32_t * pos_rows) {
     if (T < 1 || T > B200_ATTN_MAX_ROWS) B200_REFUSE(B200_ERR_SHAPE, "attn_decode: unsupported row count %d", T);
     if (!out) B200_REFUSE(B200_ERR_SHAPE, "attn_decode: out is null");
-    const int max_n = c ? c->n_ctx : 1;
+    const int n_ctx = c ? std::max(c->n_ctx, 1) : 1;
+    // the grid covers the rows' keys when the host knows them, else the cache's capacity
+    const int max_n = (!p0_dev && !pos_rows && p0 >= 0) ? std::min(std::max(p0 + T, 1), c && !c->pt ? n_ctx : 0x7fffffff) : n_ctx;
+    // the first call per (device, stream) sizes the scratch for the largest call these entry points accept on this cache
+    // (B200_ATTN_MAX_ROWS rows over n_ctx keys), as the reference does (src/fast/attn_dec2.cu:503-517)
+    size_t hint = 0;
+    if (c && c->Hkv > 0) {
+        dec_geom gm;
+        if (decode_geometry(gm, B200_ATTN_MAX_ROWS, 1, n_ctx, n_ctx, c->Hkv, 0)) hint = gm.part_floats + gm.list_ints;
+    }
+    const merge_out mo = {out, nullptr, nullptr, nullptr, nullptr, nullptr};
     // rows of one sequence at consecutive positions share the pass over its KV (up to 4 rows per slot)
     if (!pos_rows && T <= B200_MAX_QLEN)
-        return decode_impl(q, c, out, nullptr, nullptr, nullptr, nullptr, 1, T, nullptr, p0_dev, p0, max_n, Hq, scale, 0,
-                           (cudaStream_t) stream, "attn_decode");
-    return decode_impl(q, c, out, nullptr, nullptr, nullptr, nullptr, T, 1, pos_rows, p0_dev, p0, max_n, Hq, scale, 0,
-                       (cudaStream_t) stream, "attn_decode");
+        return decode_impl(q, c, mo, 1, T, nullptr, p0_dev, p0, max_n, Hq, scale, 0, (cudaStream_t) stream, "attn_decode", hint);
+    return decode_impl(q, c, mo, T, 1, pos_rows, p0_dev, p0, max_n, Hq, scale, 0, (cudaStream_t) stream, "attn_decode", hint);
 }
 
 int b200_attn_decode(const float * q, const b200_kv_cache * c, float * out, int T, int p0, int Hq, float scale, void * stream) {
@@ -1009,9 +1189,20 @@ int b200_attn_decode(const float * q, const b200_kv_cache * c, float * out, int 
 }
 int b200_attn_decode_dev(const float * q, const b200_kv_cache * c, float * out, int T, const int32_t * p0_dev, int max_n, int Hq,
                          float scale, void * stream) {
-    (void) max_n;
     if (!p0_dev) B200_REFUSE(B200_ERR_SHAPE, "attn_decode_dev: p0_dev is null");
-    return b200_attn_decode2(q, c, out, T, 0, p0_dev, Hq, scale, stream, nullptr);
+    if (T < 1 || T > B200_ATTN_MAX_ROWS) B200_REFUSE(B200_ERR_SHAPE, "attn_decode: unsupported row count %d", T);
+    if (!out) B200_REFUSE(B200_ERR_SHAPE, "attn_decode_dev: out is null");
+    const int n_ctx = c ? std::max(c->n_ctx, 1) : 1;
+    if (max_n < 1 || (c && !c->pt && max_n > n_ctx)) max_n = n_ctx;   // the caller's bound on *p0_dev + T sizes the grid
+    size_t hint = 0;
+    if (c && c->Hkv > 0) {
+        dec_geom gm;
+        if (decode_geometry(gm, B200_ATTN_MAX_ROWS, 1, n_ctx, n_ctx, c->Hkv, 0)) hint = gm.part_floats + gm.list_ints;
+    }
+    const merge_out mo = {out, nullptr, nullptr, nullptr, nullptr, nullptr};
+    if (T <= B200_MAX_QLEN)
+        return decode_impl(q, c, mo, 1, T, nullptr, p0_dev, 0, max_n, Hq, scale, 0, (cudaStream_t) stream, "attn_decode_dev", hint);
+    return decode_impl(q, c, mo, T, 1, nullptr, p0_dev, 0, max_n, Hq, scale, 0, (cudaStream_t) stream, "attn_decode_dev", hint);
 }
 int b200_attn_decode_rows(const float * q, const b200_kv_cache * c, float * out, int T, const int32_t * pos, int Hq, float scale,
                           void * stream) {
@@ -1022,8 +1213,15 @@ int b200_attn_decode_rows(const float * q, const b200_kv_cache * c, float * out,
 int b200_attn_decode_slots(const float * q, const b200_kv_cache * c, float * out, const float * gate, int n_slots, int q_len,
                            const int32_t * pos, int max_n, int Hq, float scale, int chunk_keys, void * stream) {
     if (!pos || !out) B200_REFUSE(B200_ERR_SHAPE, "attn_decode_slots: pos / out is null");
-    return decode_impl(q, c, out, gate, nullptr, nullptr, nullptr, n_slots, q_len, pos, nullptr, 0, max_n, Hq, scale, chunk_keys,
-                       (cudaStream_t) stream, "attn_decode_slots");
+    const merge_out mo = {out, gate, nullptr, nullptr, nullptr, nullptr};
+    return decode_impl(q, c, mo, n_slots, q_len, pos, nullptr, 0, max_n, Hq, scale, chunk_keys, (cudaStream_t) stream, "attn_decode_slots");
+}
+
+int b200_attn_decode_slots_a16(const float * q, const b200_kv_cache * c, float * out, const float * gate, void * qbuf, int n_slots,
+                               int q_len, const int32_t * pos, int max_n, int Hq, float scale, int chunk_keys, void * stream) {
+    if (!pos || !out || !qbuf) B200_REFUSE(B200_ERR_SHAPE, "attn_decode_slots_a16: pos / out / qbuf is null");
+    const merge_out mo = {out, gate, nullptr, nullptr, nullptr, qbuf};
+    return decode_impl(q, c, mo, n_slots, q_len, pos, nullptr, 0, max_n, Hq, scale, chunk_keys, (cudaStream_t) stream, "attn_decode_slots_a16");
 }
 
 int b200_attn_decode_slots_partial(const float * q, const b200_kv_cache * c, float * part_o, float * part_m, float * part_l,
@@ -1031,8 +1229,9 @@ int b200_attn_decode_slots_partial(const float * q, const b200_kv_cache * c, flo
                                    void * stream) {
     if (!pos || !part_o || !part_m || !part_l) B200_REFUSE(B200_ERR_SHAPE, "attn_decode_slots_partial: null argument");
     if (!aligned16(part_o)) B200_REFUSE(B200_ERR_SHAPE, "attn_decode_slots_partial: part_o must be 16-byte aligned");
-    return decode_impl(q, c, nullptr, nullptr, part_o, part_m, part_l, n_slots, q_len, pos, nullptr, 0, max_n, Hq, scale,
-                       chunk_keys, (cudaStream_t) stream, "attn_decode_slots_partial");
+    const merge_out mo = {nullptr, nullptr, part_o, part_m, part_l, nullptr};
+    return decode_impl(q, c, mo, n_slots, q_len, pos, nullptr, 0, max_n, Hq, scale, chunk_keys, (cudaStream_t) stream,
+                       "attn_decode_slots_partial");
 }
 
 int b200_attn_merge_gate(const float * part_o, const float * part_m, const float * part_l, int nparts, int R, int D,
@@ -1040,16 +1239,15 @@ int b200_attn_merge_gate(const float * part_o, const float * part_m, const float
     if (!part_o || !part_m || !part_l || !out || nparts < 1 || R < 1 || D % 4 || D < 4 || D > 4096 || !aligned16(part_o) ||
         !aligned16(out) || (gate && !aligned16(gate)))
         B200_REFUSE(B200_ERR_SHAPE, "attn_merge_gate: unsupported arguments");
-    merge_parts_k<<<R, D / 4, 0, (cudaStream_t) stream>>>(part_o, part_m, part_l, nparts, R, D, gate, out, (size_t) R * D, (size_t) R);
+    merge_parts_k<<<R, D / 4, 0, (cudaStream_t) stream>>>(part_o, part_m, part_l, nparts, R, D, gate, out, (size_t) R * D, (size_t) R,
+                                                          nullptr);
     count_launch();
     return launch_status("attn_merge_gate");
 }
 
-// The exchange step of the sequence split for a host that drives NCCL itself.  ncclAllGather is taken from the NCCL library
-// the process has already loaded (the host's own, or the one bundled with its framework), so the communicator and the
-// function come from the same library; nothing here links NCCL.
-int b200_seq_exchange_merge(void * nccl_comm, int n_seq, const float * send, float * recv, int R, int D, const float * gate,
-                            float * out, void * stream) {
+// shared by the two exchange entries: optional all-gather over the caller's communicator, then the merge
+static int seq_exchange_impl(void * nccl_comm, int n_seq, const float * send, float * recv, int R, int D, const float * gate,
+                             float * out, void * qbuf, void * stream, const char * who) {
     using allgather_fn = int (*)(const void *, void *, size_t, int, void *, cudaStream_t);
     static allgather_fn allgather = [] {
         void * f = dlsym(RTLD_DEFAULT, "ncclAllGather");
@@ -1062,17 +1260,33 @@ int b200_seq_exchange_merge(void * nccl_comm, int n_seq, const float * send, flo
     const size_t part = (size_t) R * (D + 2);
     if (!send || !recv || !out || n_seq < 1 || R < 1 || D % 4 || D < 4 || D > 4096 || part % 4 || !aligned16(send) || !aligned16(recv) ||
         !aligned16(out) || (gate && !aligned16(gate)))
-        B200_REFUSE(B200_ERR_SHAPE, "seq_exchange_merge: unsupported arguments (R * (D + 2) must be a multiple of 4, buffers 16-byte aligned)");
+        B200_REFUSE(B200_ERR_SHAPE, "%s: unsupported arguments (R * (D + 2) must be a multiple of 4, buffers 16-byte aligned)", who);
+    if (qbuf && (D % 128 || ((uintptr_t) qbuf & 3)))
+        B200_REFUSE(B200_ERR_SHAPE, "%s: the a16 buffer needs D %% 128 == 0 and 4-byte alignment", who);
     cudaStream_t s = (cudaStream_t) stream;
     const float * parts = n_seq > 1 ? recv : send;
     if (n_seq > 1 && nccl_comm) {   // without a communicator the caller has gathered the parts into recv already
-        if (!allgather) B200_REFUSE(B200_ERR_CUDA, "seq_exchange_merge: no NCCL library is loaded in this process");
+        if (!allgather) B200_REFUSE(B200_ERR_CUDA, "%s: no NCCL library is loaded in this process", who);
         const int rc = allgather(send, recv, part, 7 /* ncclFloat32 */, nccl_comm, s);
-        if (rc != 0) B200_REFUSE(B200_ERR_CUDA, "seq_exchange_merge: ncclAllGather returned %d", rc);
+        if (rc != 0) B200_REFUSE(B200_ERR_CUDA, "%s: ncclAllGather returned %d", who, rc);
     }
-    merge_parts_k<<<R, D / 4, 0, s>>>(parts, parts + (size_t) R * D, parts + (size_t) R * D + R, n_seq, R, D, gate, out, part, part);
+    merge_parts_k<<<R, D / 4, 0, s>>>(parts, parts + (size_t) R * D, parts + (size_t) R * D + R, n_seq, R, D, gate, out, part, part,
+                                      (__half2 *) qbuf);
     count_launch();
-    return launch_status("seq_exchange_merge");
+    return launch_status(who);
+}
+
+// The exchange step of the sequence split for a host that drives NCCL itself.  ncclAllGather is taken from the NCCL library
+// the process has already loaded (the host's own, or the one bundled with its framework), so the communicator and the
+// function come from the same library; nothing here links NCCL.
+int b200_seq_exchange_merge(void * nccl_comm, int n_seq, const float * send, float * recv, int R, int D, const float * gate,
+                            float * out, void * stream) {
+    return seq_exchange_impl(nccl_comm, n_seq, send, recv, R, D, gate, out, nullptr, stream, "seq_exchange_merge");
+}
+int b200_seq_exchange_merge_a16(void * nccl_comm, int n_seq, const float * send, float * recv, int R, int D, const float * gate,
+                                float * out, void * qbuf, void * stream) {
+    if (!qbuf) B200_REFUSE(B200_ERR_SHAPE, "seq_exchange_merge_a16: qbuf is null");
+    return seq_exchange_impl(nccl_comm, n_seq, send, recv, R, D, gate, out, qbuf, stream, "seq_exchange_merge_a16");
 }
 
 }  // extern "C"

@@ -12,7 +12,26 @@ torch.distributed is used for the process group and the all-gather only; all ari
 """
 import numpy as np
 
-from . import pool as P
+
+def seq_local_positions(pos, n_seq, seq_rank, psh=8):
+    """Global row positions -> positions in shard seq_rank's compacted sequence (the mapping the library's pool applies in
+    b200_pool_step).  The pages of a sequence are dealt round-robin: shard r keeps logical pages r, r + n_seq, ... back to
+    back, so global position p (page g = p >> psh, offset o) sits at local page g // n_seq, offset o, if g % n_seq == r.
+    A row at global position P sees global keys 0..P; on this shard these are the local positions 0..local(P'), P' being
+    the last owned position <= P.  Returns that last visible local position per row, -1 when the shard owns none."""
+    pos = np.asarray(pos, np.int64)
+    ps = 1 << psh
+    g = pos >> psh
+    o = pos & (ps - 1)
+    full_before = np.maximum((g - seq_rank + n_seq - 1) // n_seq, 0)   # owned pages with index < g
+    owns = (g % n_seq) == seq_rank
+    loc = np.where(owns, full_before * ps + o, full_before * ps - 1)
+    return np.where(pos < 0, -1, loc).astype(np.int32)
+
+
+def seq_local_length(n, n_seq, seq_rank, psh=8):
+    """number of positions of a sequence of n positions that live on shard seq_rank"""
+    return 0 if n <= 0 else int(seq_local_positions(np.array([n - 1]), n_seq, seq_rank, psh)[0]) + 1
 
 
 class ShardPlan:
@@ -45,10 +64,10 @@ class ShardPlan:
         return [[h * self.n_seq + s for s in range(self.n_seq)] for h in range(self.n_head_shards)]
 
     def local_positions(self, pos, psh=8):
-        return P.local_positions(pos, self.n_seq, self.seq_rank, psh)
+        return seq_local_positions(pos, self.n_seq, self.seq_rank, psh)
 
     def local_length(self, n, psh=8):
-        return P.local_length(n, self.n_seq, self.seq_rank, psh)
+        return seq_local_length(n, self.n_seq, self.seq_rank, psh)
 
 
 class SeqMerge:

@@ -92,6 +92,21 @@ def attn_decode_slots(q, c, out, gate, n_slots, q_len, pos, max_n, Hq, scale, ch
                                            max_n, Hq, scale, chunk_keys, _stream(s)) == L.OK
 
 
+def attn_decode_slots_a16(q, c, out, gate, qbuf, n_slots, q_len, pos, max_n, Hq, scale, chunk_keys=0, s=None):
+    """attn_decode_slots that also emits the a16 copy of the gated output (input format of the next projection)"""
+    return L.load().b200_attn_decode_slots_a16(L.ptr(q), C.byref(c.c()), L.ptr(out), L.ptr(gate), L.ptr(qbuf), n_slots, q_len,
+                                               L.ptr(pos), max_n, Hq, scale, chunk_keys, _stream(s)) == L.OK
+
+
+def attn_decode_slots_noalloc(q, c, out, gate, n_slots, q_len, pos, max_n, Hq, scale, chunk_keys=0, s=None):
+    return L.load().b200_attn_decode_slots_noalloc(L.ptr(q), C.byref(c.c()), L.ptr(out), L.ptr(gate), n_slots, q_len, L.ptr(pos),
+                                                   max_n, Hq, scale, chunk_keys, _stream(s))
+
+
+def attn_reserve(max_slots, q_len, max_n, n_ctx, Hkv, chunk_keys=0, s=None):
+    return L.load().b200_attn_reserve(max_slots, q_len, max_n, n_ctx, Hkv, chunk_keys, _stream(s)) == L.OK
+
+
 def attn_decode_slots_partial(q, c, part_o, part_m, part_l, n_slots, q_len, pos, max_n, Hq, scale, chunk_keys=0, s=None):
     return L.load().b200_attn_decode_slots_partial(L.ptr(q), C.byref(c.c()), L.ptr(part_o), L.ptr(part_m), L.ptr(part_l),
                                                    n_slots, q_len, L.ptr(pos), max_n, Hq, scale, chunk_keys,
@@ -107,6 +122,11 @@ def seq_exchange_merge(nccl_comm, n_seq, send, recv, R, D, gate, out, s=None):
     """all-gather of the shards' flat partials over the caller's ncclComm_t (an integer address) + merge + gate"""
     return L.load().b200_seq_exchange_merge(C.c_void_p(nccl_comm), n_seq, L.ptr(send), L.ptr(recv), R, D, L.ptr(gate),
                                             L.ptr(out), _stream(s)) == L.OK
+
+
+def seq_exchange_merge_a16(nccl_comm, n_seq, send, recv, R, D, gate, out, qbuf, s=None):
+    return L.load().b200_seq_exchange_merge_a16(C.c_void_p(nccl_comm), n_seq, L.ptr(send), L.ptr(recv), R, D, L.ptr(gate),
+                                                L.ptr(out), L.ptr(qbuf), _stream(s)) == L.OK
 
 
 def attn_prefill(q, c, out, T, p0, Hq, scale, s=None):
@@ -125,6 +145,29 @@ def attn_fold(q, c, out, T, p0, Hq, scale, scratch, scratch_bytes, s=None, chunk
 def attn_prefill_gated(q, c, out, gate, T, p0, Hq, scale, scratch, scratch_bytes, s=None):
     return L.load().b200_attn_prefill_gated(L.ptr(q), C.byref(c.c()), L.ptr(out), L.ptr(gate), T, p0, Hq, scale,
                                             L.ptr(scratch), scratch_bytes, _stream(s)) == L.OK
+
+
+def attn_prefill_gated_a16(q, c, out, gate, qbuf, T, p0, Hq, scale, scratch, scratch_bytes, s=None):
+    return L.load().b200_attn_prefill_gated_a16(L.ptr(q), C.byref(c.c()), L.ptr(out), L.ptr(gate), L.ptr(qbuf), T, p0, Hq, scale,
+                                                L.ptr(scratch), scratch_bytes, _stream(s)) == L.OK
+
+
+def attn_prefill_bf16_scratch_bytes(T, Hkv, pass_keys=0, out_is_bf16=False):
+    return L.load().b200_attn_prefill_bf16_scratch_bytes(T, Hkv, pass_keys, 1 if out_is_bf16 else 0)
+
+
+def attn_prefill_bf16(q, k, v, gate_f32, gate_bf16, out_f32, out_bf16, qbuf, c, p0, T, Hq, n_rot, freq_base, scale, scratch,
+                      scratch_bytes, s=None):
+    """rope + quantise + append of K/V and gated causal attention over bf16 q in one call (see include/b200attn.h)"""
+    return L.load().b200_attn_prefill_bf16(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(gate_f32), L.ptr(gate_bf16), L.ptr(out_f32),
+                                           L.ptr(out_bf16), L.ptr(qbuf), C.byref(c.c()), p0, T, Hq, n_rot, freq_base, scale,
+                                           L.ptr(scratch), scratch_bytes, _stream(s)) == L.OK
+
+
+def attn_prefill_partial(q, c, part_o, part_m, part_l, last_key, max_keys, T, Hq, scale, scratch, scratch_bytes, s=None):
+    return L.load().b200_attn_prefill_partial(L.ptr(q), C.byref(c.c()), L.ptr(part_o), L.ptr(part_m), L.ptr(part_l),
+                                              L.ptr(last_key), max_keys, T, Hq, scale, L.ptr(scratch), scratch_bytes,
+                                              _stream(s)) == L.OK
 
 
 def attn_prep(qg, k, v, q_norm, k_norm, pos, q, gate, c, p0, T, Hq, Hkv, D, n_rot, freq_base, eps, s=None, ldq=0, ldk=0,
@@ -159,6 +202,15 @@ def ew_quant(op, a, b, y, qbuf, T, n, s=None, lda=0, ldb=0):
 
 def kv_fill_random(c, p0, p1, seed, s=None):
     return L.load().b200_kv_fill_random(C.byref(c.c()), p0, p1, seed, _stream(s)) == L.OK
+
+
+def kv_fill_slots(c, n_slots, lens, table_stride, seed, head0=0, n_seq=1, seq_rank=0, s=None):
+    return L.load().b200_kv_fill_slots(C.byref(c.c()), n_slots, L.ptr(lens), table_stride, seed, head0, n_seq, seq_rank,
+                                       _stream(s)) == L.OK
+
+
+def noalloc_device_status(s=None):
+    return L.load().b200_noalloc_device_status(_stream(s))
 
 
 def device_status(s=None):

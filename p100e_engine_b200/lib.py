@@ -12,7 +12,7 @@ LIB_PATH = os.environ.get("B200ATTN_LIB") or os.path.join(HERE, "libb200attn.so"
 KV_F16, KV_Q4_0, KV_Q8_0 = 1, 2, 8
 ATTN_MAX_ROWS = 8
 MAX_QLEN = 4
-OK, ERR_SHAPE, ERR_ALLOC, ERR_CUDA, ERR_SCRATCH, ERR_DEVICE = range(6)
+OK, ERR_SHAPE, ERR_ALLOC, ERR_CUDA, ERR_SCRATCH, ERR_DEVICE, ERR_FORMAT, ERR_IO = range(8)
 
 
 class KvCache(C.Structure):
@@ -20,6 +20,9 @@ class KvCache(C.Structure):
     _fields_ = [("type", C.c_uint32), ("n_ctx", C.c_int32), ("Hkv", C.c_int32), ("D", C.c_int32),
                 ("k", C.c_void_p), ("v", C.c_void_p), ("pt", C.c_void_p), ("rtab", C.c_void_p),
                 ("psh", C.c_int32), ("pstride", C.c_size_t)]
+
+    def c(self):   # the host-side mirror's kv_cache objects convert themselves with c(); a struct is already one
+        return self
 
 
 class MropePos(C.Structure):
@@ -42,6 +45,7 @@ SIGNATURES = {
     "b200_kv_alloc": (I, [KVP, U32, I, I, I]),
     "b200_kv_free": (None, [KVP]),
     "b200_kv_fill_random": (I, [KVP, I, I, U32, P]),
+    "b200_kv_fill_slots": (I, [KVP, I, P, I, U32, I, I, I, P]),
     "b200_kv_append": (I, [KVP, P, P, I, I, P]),
     "b200_kv_append_dev": (I, [KVP, P, P, P, I, P]),
     "b200_attn_prep": (I, [P, P, P, P, P, P, P, P, KVP, I, I, I, I, I, I, F, F, P, I, I, I, C.POINTER(MropePos)]),
@@ -54,19 +58,53 @@ SIGNATURES = {
     "b200_attn_dec2_nsplit": (I, [I]),
     "b200_attn_dec2_set_nsplit": (None, [I]),
     "b200_attn_dec2_reload_env": (I, []),
+    "b200_attn_fixed_chunk": (I, [I]),
+    "b200_attn_reserve": (I, [I, I, I, I, I, I, P]),
     "b200_attn_decode_slots": (I, [P, KVP, P, P, I, I, P, I, I, F, I, P]),
+    "b200_attn_decode_slots_a16": (I, [P, KVP, P, P, P, I, I, P, I, I, F, I, P]),
+    "b200_noalloc_device_status": (I, [P]),
     "b200_attn_decode_slots_noalloc": (I, [P, KVP, P, P, I, I, P, I, I, F, I, P]),
     "b200_attn_decode_slots_partial": (I, [P, KVP, P, P, P, I, I, P, I, I, F, I, P]),
     "b200_attn_merge_gate": (I, [P, P, P, I, I, I, P, P, P]),
     "b200_seq_exchange_merge": (I, [P, I, P, P, I, I, P, P, P]),
+    "b200_seq_exchange_merge_a16": (I, [P, I, P, P, I, I, P, P, P, P]),
     "b200_attn_chunk_keys": (I, []),
     "b200_attn_prefill": (I, [P, KVP, P, I, I, I, F, P]),
     "b200_attn_prefill_variant": (I, [P, KVP, P, I, I, I, F, P, I]),
     "b200_attn_fold_scratch_bytes": (SZ, [I, I, I, I]),
     "b200_attn_fold": (I, [P, KVP, P, I, I, I, F, P, SZ, P, I, I]),
     "b200_attn_prefill_gated": (I, [P, KVP, P, P, I, I, I, F, P, SZ, P]),
+    "b200_attn_prefill_gated_a16": (I, [P, KVP, P, P, P, I, I, I, F, P, SZ, P]),
+    "b200_attn_prefill_bf16_scratch_bytes": (SZ, [I, I, I, I]),
+    "b200_attn_prefill_bf16": (I, [P, P, P, P, P, P, P, P, KVP, I, I, I, I, F, F, P, SZ, P]),
+    "b200_attn_prefill_partial": (I, [P, KVP, P, P, P, P, I, I, I, F, P, SZ, P]),
     "b200_sigmoid_mul": (I, [P, P, I64, P]),
     "b200_ew_quant": (I, [I, P, P, P, P, I, I, P, I, I]),
+    "b200_pool_create": (P, [U32, I, I, I, I, I, I, I, I, U32, I, I, I]),
+    "b200_pool_destroy": (None, [P]),
+    "b200_pool_bytes": (SZ, [P]),
+    "b200_pool_base": (P, [P]),
+    "b200_pool_free_pages": (I, [P]),
+    "b200_pool_slot_pages": (I, [P, I]),
+    "b200_pool_table_host": (P, [P]),
+    "b200_pool_local_length": (I, [P, I]),
+    "b200_pool_ensure": (I, [P, I, I, P]),
+    "b200_pool_release": (I, [P, I, P]),
+    "b200_pool_view": (I, [P, I, I, KVP]),
+    "b200_pool_step": (I, [P, P, P, I, I, I, P]),
+    "b200_pool_step_rope_pos": (P, [P]),
+    "b200_pool_step_last_key": (P, [P]),
+    "b200_pool_step_cache_row": (P, [P]),
+    "b200_pool_step_rtab": (P, [P]),
+    "b200_pool_step_rows": (I, [P]),
+    "b200_pool_step_max_n": (I, [P]),
+    "b200_pool_page_bytes": (SZ, [P]),
+    "b200_pool_pages_out": (I, [P, I, I, I, P, P]),
+    "b200_pool_pages_in": (I, [P, I, I, I, P, P]),
+    "b200_session_write_header": (I, [I, P, I, P, I, I]),
+    "b200_session_write_rank": (I, [I, P, I, I, P, SZ, P]),
+    "b200_session_read_header": (I, [I, P, I, I, I, P, P, P, P, I, P]),
+    "b200_session_read_rank": (I, [I, P, I, I, P, SZ, P]),
     "b200_last_device_status": (I, [P]),
     "b200_launch_count": (C.c_uint64, []),
     "b200_version": (C.c_char_p, []),

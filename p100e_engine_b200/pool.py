@@ -1,14 +1,13 @@
-"""Paged KV pool, block tables and step descriptors — the caller-side structures the attention kernels index.
+"""Python mirror of the library's paged-KV pool (b200_pool_* / b200_session_* in include/b200attn.h).
 
-Mirrors what the reference engine keeps in tp_model (reference src/tp_model.cu): one allocation per GPU laid out
-[K|V][kv layer][page][2^psh positions][row] (alloc_pool, :3875-3966), a page table ptab[max_slots][max_pages] of int32
-page ids filled from a free list (ensure_pages, :3358-3384), and per step a descriptor of row positions and per-row
-table offsets rtab[row] = slot * max_pages (forward_batch_ids, :3999-4022).  Differences: offsets are 64-bit (a layer
-region may exceed 4 GiB), a step may hold any number of rows, and a sequence-shard map says which GPU of a pair owns
-each page when the KV sequence is split across two GPUs.
-
-Pure host logic (numpy); device buffers are attached by the caller (torch tensors), so this module runs without a GPU.
+The pool, its page tables, the step descriptor, the page offload layout and the sequence file format are host C++ inside
+libb200attn.so (csrc/kv_pool.cu), standing for what the reference engine keeps in tp_model (reference src/tp_model.cu:
+alloc_pool :3880-3966, ensure_pages :3358-3384, forward_batch_ids :3999-4022, kv_seq / kv_rows :3327-3337, seq_offload
+:3432-3481, seq_write / seq_read :3738-3862).  This module only forwards to it; `device=-1` keeps a pool in host memory,
+which is how the CPU tests drive the same code.
 """
+import ctypes as C
+
 import numpy as np
 
 from . import lib as L
@@ -17,96 +16,139 @@ HEAD_BYTES = {L.KV_F16: 512, L.KV_Q8_0: 272, L.KV_Q4_0: 144}   # D = 256
 
 
 def row_bytes(kv_type, hkv, d=256):
-    per32 = {L.KV_F16: 64, L.KV_Q8_0: 34, L.KV_Q4_0: 18}[kv_type]
-    return hkv * (d // 32) * per32
+    return L.load().b200_kv_row_bytes(kv_type, hkv, d)
 
 
-class PoolLayout:
-    """Byte layout of one GPU's pool: [K|V][layer][page][2^psh][row]."""
+def _i32(a):
+    return np.ascontiguousarray(np.asarray(a, dtype=np.int32))
 
-    def __init__(self, kv_type, hkv, n_layers, n_pages, psh=8, d=256):
+
+class Pool:
+    """One GPU's (or, with device=-1, a host-memory) pool [K|V][layer][page][2^psh][row] with its page table."""
+
+    def __init__(self, kv_type, hkv, n_layers, n_pages, psh=8, d=256, max_slots=1, max_pages=1, max_rows=1, seed=0, n_seq=1,
+                 seq_rank=0, device=-1):
+        self.lib = L.load()
+        self.h = self.lib.b200_pool_create(kv_type, hkv, d, n_layers, n_pages, psh, max_slots, max_pages, max_rows, seed, n_seq,
+                                           seq_rank, device)
+        if not self.h:
+            raise RuntimeError("b200_pool_create refused")
         self.kv_type, self.hkv, self.d, self.n_layers, self.n_pages, self.psh = kv_type, hkv, d, n_layers, n_pages, psh
-        self.page_positions = 1 << psh
+        self.max_slots, self.max_pages, self.max_rows, self.device = max_slots, max_pages, max_rows, device
         self.rowb = row_bytes(kv_type, hkv, d)
-        self.pstride = self.page_positions * self.rowb          # bytes between consecutive pages of one layer's K
-        self.layer_bytes = n_pages * self.pstride
-        self.total_bytes = 2 * n_layers * self.layer_bytes
+        self.pstride = self.rowb << psh
+        self.total_bytes = self.lib.b200_pool_bytes(self.h)
+        self.page_bytes = self.lib.b200_pool_page_bytes(self.h)
 
-    def k_offset(self, layer):
-        return layer * self.layer_bytes
+    def close(self):
+        if self.h:
+            self.lib.b200_pool_destroy(self.h)
+            self.h = None
 
-    def v_offset(self, layer):
-        return (self.n_layers + layer) * self.layer_bytes
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ---- tables
+    def table(self):
+        """host copy of ptab[max_slots][max_pages] (a view of the library's pinned memory; -1 = unset)"""
+        p = self.lib.b200_pool_table_host(self.h)
+        return np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_int32)), shape=(self.max_slots, self.max_pages))
+
+    def free_pages(self):
+        return self.lib.b200_pool_free_pages(self.h)
+
+    def slot_pages(self, slot):
+        return self.lib.b200_pool_slot_pages(self.h, slot)
+
+    def local_length(self, n):
+        return self.lib.b200_pool_local_length(self.h, n)
+
+    def ensure(self, slot, n_positions, stream=None):
+        return self.lib.b200_pool_ensure(self.h, slot, n_positions, stream)
+
+    def release(self, slot, stream=None):
+        return self.lib.b200_pool_release(self.h, slot, stream)
+
+    def view(self, layer, slot=-1):
+        """b200_kv_cache of one layer: slot >= 0 = that sequence (kv_seq), slot < 0 = all rows of the last step (kv_rows)"""
+        c = L.KvCache()
+        L.check("b200_pool_view", self.lib.b200_pool_view(self.h, layer, slot, C.byref(c)))
+        return c
+
+    # ---- step descriptor
+    def step(self, slots, n_past, q_len, grow=True, stream=None):
+        s, n = _i32(slots), _i32(n_past)
+        return self.lib.b200_pool_step(self.h, s.ctypes.data, n.ctypes.data, len(s), q_len, 1 if grow else 0, stream)
+
+    def step_arrays(self):
+        """device (or host, for a host pool) addresses: rotary position, last visible local key, own cache row, rtab"""
+        f = self.lib
+        return (f.b200_pool_step_rope_pos(self.h), f.b200_pool_step_last_key(self.h), f.b200_pool_step_cache_row(self.h),
+                f.b200_pool_step_rtab(self.h))
+
+    def step_rows(self):
+        return self.lib.b200_pool_step_rows(self.h)
+
+    def step_max_n(self):
+        return self.lib.b200_pool_step_max_n(self.h)
+
+    def step_host(self):
+        """the four step arrays of a host-memory pool as numpy arrays (tests)"""
+        assert self.device < 0
+        r = self.step_rows()
+        return [np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_int32)), shape=(r,)).copy() for p in self.step_arrays()]
+
+    # ---- offload / files
+    def pages_out(self, slot, first, n, dst, stream=None):
+        return self.lib.b200_pool_pages_out(self.h, slot, first, n, L.ptr(dst), stream)
+
+    def pages_in(self, slot, first, n, src, stream=None):
+        return self.lib.b200_pool_pages_in(self.h, slot, first, n, L.ptr(src), stream)
+
+    def base_host(self):
+        """the pool bytes of a host-memory pool as a numpy view (tests)"""
+        assert self.device < 0
+        p = self.lib.b200_pool_base(self.h)
+        return np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_uint8)), shape=(self.total_bytes,))
+
+    def base(self):
+        return self.lib.b200_pool_base(self.h)
 
 
-class PageTable:
-    """ptab[max_slots][max_pages] with a free list; pages are handed out in a seeded random order so that physical
-    placement is scattered the way a long-running server's is."""
-
-    def __init__(self, n_pages, max_slots, max_pages, psh=8, seed=0):
-        self.psh, self.max_slots, self.max_pages = psh, max_slots, max_pages
-        self.ptab = np.full((max_slots, max_pages), -1, np.int32)
-        self.n_alloc = np.zeros(max_slots, np.int32)
-        self.free = list(np.random.default_rng(seed).permutation(n_pages).astype(np.int32))[::-1]
-
-    def ensure_pages(self, slot, n_positions):
-        """make positions [0, n_positions) of the slot addressable; returns False when the pool is exhausted"""
-        need = (n_positions + (1 << self.psh) - 1) >> self.psh
-        if need > self.max_pages:
-            return False
-        while self.n_alloc[slot] < need:
-            if not self.free:
-                return False
-            self.ptab[slot, self.n_alloc[slot]] = self.free.pop()
-            self.n_alloc[slot] += 1
-        return True
-
-    def release(self, slot):
-        for i in range(self.n_alloc[slot]):
-            self.free.append(self.ptab[slot, i])
-        self.ptab[slot, :] = -1
-        self.n_alloc[slot] = 0
+def session_write(fd, fingerprint, n_past, tokens, pools_slots, states=None, stream=None):
+    """one sequence file: header, then every (pool, slot) block in rank order with its opaque state bytes"""
+    lib = L.load()
+    fp = np.ascontiguousarray(np.asarray(fingerprint, dtype=np.uint64))
+    assert fp.shape == (15,)
+    tok = _i32(tokens)
+    pages = pools_slots[0][0].slot_pages(pools_slots[0][1])
+    rc = lib.b200_session_write_header(fd, fp.ctypes.data, n_past, tok.ctypes.data, len(tok), pages)
+    for i, (pool, slot) in enumerate(pools_slots):
+        if rc != L.OK:
+            break
+        st = states[i] if states else b""
+        rc = lib.b200_session_write_rank(fd, pool.h, slot, pool.slot_pages(slot), C.c_char_p(st) if st else None, len(st), stream)
+    return rc
 
 
-def step_descriptor(slots, n_past, q_len, max_pages):
-    """Rows of one decode / verify step, slot-major: row r = i * q_len + j is token j of slots[i] at position
-    n_past[i] + j and reads the table at rtab[r] = slots[i] * max_pages.  Returns (pos, rtab) int32 arrays."""
-    slots = np.asarray(slots, np.int64)
-    n_past = np.asarray(n_past, np.int64)
-    j = np.arange(q_len, dtype=np.int64)
-    pos = (n_past[:, None] + j[None, :]).reshape(-1).astype(np.int32)
-    rtab = np.repeat(slots * max_pages, q_len).astype(np.int32)
-    return pos, rtab
-
-
-# ---- sequence sharding over a pair of GPUs ----------------------------------------------------------------------
-def seq_shard_owner(page_index, n_seq):
-    """which of the n_seq sequence shards owns logical page `page_index` of a sequence: pages are dealt round-robin,
-    so the shards stay balanced at every depth and an appended token lands on the shard that owns its page"""
-    return page_index % n_seq
-
-
-def local_positions(pos, n_seq, seq_rank, psh=8):
-    """Global row positions -> positions in shard seq_rank's compacted sequence.
-
-    Shard r keeps logical pages r, r + n_seq, ... back to back, so global position p (page g = p >> psh, offset o)
-    sits at local page g // n_seq, offset o, if g % n_seq == r.  A row at global position P sees global keys 0..P; on
-    this shard these are the local positions 0..local(P'), P' being the last owned position <= P.  Returns the local
-    position of that last visible key per row, -1 when the shard owns no visible key."""
-    pos = np.asarray(pos, np.int64)
-    ps = 1 << psh
-    g = pos >> psh
-    o = pos & (ps - 1)
-    full_before = (g - seq_rank + n_seq - 1) // n_seq            # owned pages with index < g
-    full_before = np.maximum(full_before, 0)
-    owns = (g % n_seq) == seq_rank
-    loc = np.where(owns, full_before * ps + o, full_before * ps - 1)
-    loc = np.where(pos < 0, -1, loc)
-    return loc.astype(np.int32)
-
-
-def local_length(n, n_seq, seq_rank, psh=8):
-    """number of positions of a sequence of n positions that live on shard seq_rank"""
-    if n <= 0:
-        return 0
-    return int(local_positions(np.array([n - 1]), n_seq, seq_rank, psh)[0]) + 1
+def session_read(fd, fingerprint, max_ctx, pools_slots, state_bytes=None, stream=None):
+    """reads a sequence file into the given (pool, free slot) pairs; returns (status, n_past, tokens, states, bad_field)"""
+    lib = L.load()
+    fp = np.ascontiguousarray(np.asarray(fingerprint, dtype=np.uint64))
+    pool0 = pools_slots[0][0]
+    n_past, n_tok, pages, bad = C.c_int(), C.c_int(), C.c_int(), C.c_int(-1)
+    tok = np.zeros(max(max_ctx, 1), np.int32)
+    rc = lib.b200_session_read_header(fd, fp.ctypes.data, max_ctx, pool0.max_pages, pool0.psh, C.byref(n_past), C.byref(n_tok),
+                                      C.byref(pages), tok.ctypes.data, len(tok), C.byref(bad))
+    states = []
+    for i, (pool, slot) in enumerate(pools_slots):
+        if rc != L.OK:
+            break
+        nb = state_bytes[i] if state_bytes else 0
+        buf = C.create_string_buffer(nb) if nb else None
+        rc = lib.b200_session_read_rank(fd, pool.h, slot, pages.value, buf, nb, stream)
+        states.append(buf.raw if buf else b"")
+    return rc, n_past.value, tok[:n_tok.value].copy(), states, bad.value

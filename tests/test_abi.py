@@ -24,6 +24,22 @@ def test_binding_covers_header():
     assert sorted(L.SIGNATURES) == header_symbols()
 
 
+def test_shim_header_compiles_reference_call_sites():
+    """include/p100e_fast_shim.h keeps the reference's C++ signatures and defaults: a translation unit with the call forms
+    of the reference's callers (tests/cabi/shim_callsites.cpp) must compile against it"""
+    import shutil
+    import subprocess
+    cuda_inc = None
+    for cand in ("/usr/local/cuda/include", os.path.join(os.path.dirname(os.path.dirname(shutil.which("nvcc") or "/x/y")), "include")):
+        if os.path.exists(os.path.join(cand, "cuda_runtime.h")):
+            cuda_inc = cand
+            break
+    assert cuda_inc, "cuda_runtime.h not found"
+    r = subprocess.run(["g++", "-std=c++17", "-fsyntax-only", "-Wall", "-I", os.path.join(ROOT, "include"), "-I", cuda_inc,
+                        os.path.join(ROOT, "tests", "cabi", "shim_callsites.cpp")], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+
+
 def test_row_bytes(lib):
     # reference kv_row_bytes (src/fast/attn.cu:501-503): f16 2 B/value, q8_0 34 B and q4_0 18 B per 32 values
     assert lib.b200_kv_row_bytes(L.KV_F16, 4, 256) == 2048

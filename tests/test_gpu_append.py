@@ -207,8 +207,8 @@ def test_rope_append_bf16_vs_oracle(cuda, lib):
 
 @pytest.mark.parametrize("tname", ["f16", "q8_0", "q4_0"])
 def test_rope_append_bf16_row_kernel_equals_head_kernel(cuda, lib, tname):
-    """16-byte aligned inputs take the one-block-per-token kernel, inputs shifted by one element the one-block-per-head
-    kernel: same expressions, so the cache bytes and the rotated q must be identical"""
+    """16-byte aligned inputs are read with 16-byte loads, inputs shifted by one element value by value: the cache bytes
+    and the rotated q must be identical"""
     import torch
     from p100e_engine_b200 import fast
     T, p0, n_rot, base = 257, 1000, 64, 1e7

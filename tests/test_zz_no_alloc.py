@@ -47,9 +47,37 @@ def _case(cuda, lib, kt, lens, q_len, seed):
 
 
 def test_noalloc_matches_regular_entry_twice(cuda, lib):
+    import torch
     # two different calls back to back: the second one reuses the array with the first one's partials still in it
     _case(cuda, lib, TYPES["q8_0"], [1500, 300, 2049], 4, 11)
-    _case(cuda, lib, TYPES["q4_0"], [700, 64], 1, 12)
+    keep = _case(cuda, lib, TYPES["q4_0"], [700, 64], 1, 12)
+    # once the kernels are loaded, a further call leaves the device's free memory where it was, and so does reading the
+    # entry point's own status word
+    q, cs, gate, pos, n_slots, q_len, max_n = keep[:7]
+    out = torch.zeros(n_slots * q_len, HQ, D, device=cuda)
+    stream = torch.cuda.current_stream().cuda_stream
+    torch.cuda.synchronize()
+    free0 = torch.cuda.mem_get_info()[0]
+    assert lib.b200_attn_decode_slots_noalloc(q.data_ptr(), C.byref(cs), out.data_ptr(), gate.data_ptr(), n_slots, q_len,
+                                              pos.data_ptr(), max_n, HQ, SCALE, 512, stream) == 0
+    assert lib.b200_noalloc_device_status(stream) == 0
+    assert torch.cuda.mem_get_info()[0] == free0
+
+
+def test_noalloc_status_word_is_readable(cuda, lib):
+    """a position beyond max_n through this entry point lands in its own status word (bit 8), which
+    b200_noalloc_device_status returns and clears; the regular status word stays clean"""
+    import torch
+    keep = _case(cuda, lib, TYPES["q8_0"], [900], 4, 14)
+    q, cs, gate, pos, n_slots, q_len, max_n = keep[:7]
+    out = torch.full((q_len, HQ, D), float("nan"), device=cuda)
+    stream = torch.cuda.current_stream().cuda_stream
+    assert lib.b200_attn_decode_slots_noalloc(q.data_ptr(), C.byref(cs), out.data_ptr(), gate.data_ptr(), n_slots, q_len,
+                                              pos.data_ptr(), 256, HQ, SCALE, 256, stream) == 0      # claims 256 keys of 900
+    assert lib.b200_noalloc_device_status(stream) == 8
+    assert lib.b200_noalloc_device_status(stream) == 0
+    assert lib.b200_last_device_status(stream) == 0
+    assert torch.isfinite(out).all()
 
 
 def test_noalloc_rejects_oversize(cuda, lib):
