@@ -111,6 +111,12 @@ int b200_rope_append_bf16(const uint16_t *q, const uint16_t *k, const uint16_t *
                           const b200_kv_cache *c, int p0, int T, int Hq, int Hkv, int D, int n_rot, float freq_base,
                           void *stream);
 
+/* The same with the cache row and the rotary position given separately (a sequence shard stores token t at its local row
+ * row0 + t while the angle comes from the global position rope0 + t); k == v == NULL: only q is rotated. */
+int b200_rope_append_bf16_at(const uint16_t *q, const uint16_t *k, const uint16_t *v, float *q_out,
+                             const b200_kv_cache *c, int row0, int rope0, int T, int Hq, int Hkv, int D, int n_rot,
+                             float freq_base, void *stream);
+
 /* ---------------------------------------------------------------- decode / MTP verify ------------------------ */
 /* attn_decode (attn.cuh:44, attn.cu:638): q, out [T][Hq][D] f32, row t at position p0+t sees keys 0..p0+t. T <= 8. */
 int b200_attn_decode(const float *q, const b200_kv_cache *c, float *out, int T, int p0, int Hq, float scale, void *stream);
@@ -274,6 +280,8 @@ b200_pool *b200_pool_create(uint32_t kv_type, int Hkv, int D, int n_layers, int 
 void b200_pool_destroy(b200_pool *p);
 size_t b200_pool_bytes(const b200_pool *p);
 void *b200_pool_base(const b200_pool *p);
+/* raw pool bytes [offset, offset + nbytes) -> dst (host or device memory), asynchronous on the stream */
+int b200_pool_read(const b200_pool *p, size_t offset, void *dst, size_t nbytes, void *stream);
 int b200_pool_free_pages(const b200_pool *p);
 int b200_pool_slot_pages(const b200_pool *p, int slot);
 const int32_t *b200_pool_table_host(const b200_pool *p);          /* host copy of ptab[max_slots][max_pages], -1 = unset */

@@ -28,10 +28,11 @@ enum : unsigned {
 unsigned * device_status_word();          // device pointer for the current device (allocated on first use), or nullptr
 void count_launch(int n = 1);
 // bf16 token rows -> K rotated and K, V quantised into cache rows p0 + t; q (optional) rotated into fp32 q_out; cs_out
-// (optional) receives each token's cos / sin table [T][n_rot] (defined in kv_append.cu)
+// (optional) receives each token's cos / sin table [T][n_rot]; rope0 >= 0: the angles come from positions rope0 + t instead
+// of p0 + t; k == v == nullptr: only q is rotated (defined in kv_append.cu)
 int rope_append_launch(const uint16_t * q, const uint16_t * k, const uint16_t * v, float * q_out, float * cs_out,
                        const b200_kv_cache * c, int p0, int T, int Hq, int Hkv, int D, int n_rot, float freq_base, cudaStream_t s,
-                       const char * who);
+                       const char * who, int rope0 = -1);
 
 // ---- row sizes (reference: kv_row_bytes, src/fast/attn.cu:501-503) ---------------------------------------------
 __host__ __device__ constexpr int head_bytes(uint32_t type, int D = DH) {

@@ -224,12 +224,12 @@ __device__ __forceinline__ void ld_bf16x8(const __nv_bfloat16 * p, bool vec, flo
 template <uint32_t KT>
 __global__ void __launch_bounds__(ROPE_THR) rope_rows_k(const __nv_bfloat16 * __restrict__ qg, const __nv_bfloat16 * __restrict__ k,
                                                    const __nv_bfloat16 * __restrict__ v, float * __restrict__ q, float * __restrict__ cs_out,
-                                                   kv_view g, int p0, int Hq, int Hkv, int D, int n_rot, float freq_base, int vec,
-                                                   unsigned * status) {
+                                                   kv_view g, int p0, int rope0, int Hq, int Hkv, int D, int n_rot, float freq_base,
+                                                   int vec, unsigned * status) {
     extern __shared__ float smr[];   // cos[half] | sin[half] | K heads [Hkv][D]
     const int t = blockIdx.x, i = threadIdx.x, half = n_rot / 2, lane = i & 31, wid = i >> 5, nb = D / 32;
     float * cs = smr, * kb = smr + n_rot;
-    const int ppos = p0 + t;
+    const int ppos = rope0 + t;   // the angle's position; the cache row is p0 + t (they differ on a sequence shard)
     for (int j = i; j < half; j += ROPE_THR) {
         const float theta = (float) ppos * powf(freq_base, -2.0f * j / n_rot);
         const float c = cosf(theta), sn = sinf(theta);
@@ -237,7 +237,7 @@ __global__ void __launch_bounds__(ROPE_THR) rope_rows_k(const __nv_bfloat16 * __
         cs[half + j] = sn;
         if (cs_out) { cs_out[(size_t) t * n_rot + j] = c; cs_out[(size_t) t * n_rot + half + j] = sn; }
     }
-    for (int e = i; e < Hkv * D / 8; e += ROPE_THR) {
+    for (int e = i; k && e < Hkv * D / 8; e += ROPE_THR) {
         float f[8];
         ld_bf16x8(k + (size_t) t * Hkv * D + (size_t) e * 8, vec, f);
         reinterpret_cast<float4 *>(kb)[2 * e] = make_float4(f[0], f[1], f[2], f[3]);
@@ -276,6 +276,7 @@ __global__ void __launch_bounds__(ROPE_THR) rope_rows_k(const __nv_bfloat16 * __
             reinterpret_cast<float4 *>(dst + d0 + half)[1] = make_float4(y1[4], y1[5], y1[6], y1[7]);
         }
     }
+    if (!k) return;   // q only
     for (int e = i; e < Hkv * half; e += ROPE_THR) {
         const int h = e / half, j = e - h * half;
         const float c = cs[j], sn = cs[half + j];
@@ -426,9 +427,10 @@ int prep_impl(const float * qg, const float * k, const float * v, const float * 
 // bf16 rows -> K rotated, K and V quantised into rows p0 + t; q (optional) rotated to fp32 q_out; cs_out (optional) receives
 // the tokens' cos / sin table.  Shared by b200_rope_append_bf16 and the bf16 prefill entry point.
 int rope_append_launch(const uint16_t * q, const uint16_t * k, const uint16_t * v, float * q_out, float * cs_out, const b200_kv_cache * c,
-                       int p0, int T, int Hq, int Hkv, int D, int n_rot, float freq_base, cudaStream_t s, const char * who) {
+                       int p0, int T, int Hq, int Hkv, int D, int n_rot, float freq_base, cudaStream_t s, const char * who, int rope0) {
     if (T <= 0) return B200_OK;
-    if (!c || !k || !v || (q && !q_out)) B200_REFUSE(B200_ERR_SHAPE, "%s: null argument", who);
+    if (rope0 < 0) rope0 = p0;
+    if (!c || (!k != !v) || (!k && !q) || (q && !q_out)) B200_REFUSE(B200_ERR_SHAPE, "%s: null argument", who);
     if (!type_ok(c->type) || !c->k || c->D != D || c->Hkv != Hkv || D % 128 || D > 1024 || n_rot > D || n_rot % 16 || p0 < 0 ||
         (!c->pt && p0 + T > c->n_ctx) || (q_out && !aligned16(q_out)))
         B200_REFUSE(B200_ERR_SHAPE, "%s: unsupported shape / cache / alignment (D=%d Hkv=%d n_rot=%d p0=%d; n_rot must be a multiple of 16)", who, D, Hkv, n_rot, p0);
@@ -439,9 +441,9 @@ int rope_append_launch(const uint16_t * q, const uint16_t * k, const uint16_t * 
     if (!st) return B200_ERR_CUDA;
     const kv_view g = view_of(*c);
     const __nv_bfloat16 * qb = (const __nv_bfloat16 *) q, * kb = (const __nv_bfloat16 *) k, * vb = (const __nv_bfloat16 *) v;
-    if (c->type == B200_KV_F16) rope_rows_k<B200_KV_F16><<<T, ROPE_THR, smem, s>>>(qb, kb, vb, q_out, cs_out, g, p0, Hq, Hkv, D, n_rot, freq_base, vec, st);
-    else if (c->type == B200_KV_Q8_0) rope_rows_k<B200_KV_Q8_0><<<T, ROPE_THR, smem, s>>>(qb, kb, vb, q_out, cs_out, g, p0, Hq, Hkv, D, n_rot, freq_base, vec, st);
-    else rope_rows_k<B200_KV_Q4_0><<<T, ROPE_THR, smem, s>>>(qb, kb, vb, q_out, cs_out, g, p0, Hq, Hkv, D, n_rot, freq_base, vec, st);
+    if (c->type == B200_KV_F16) rope_rows_k<B200_KV_F16><<<T, ROPE_THR, smem, s>>>(qb, kb, vb, q_out, cs_out, g, p0, rope0, Hq, Hkv, D, n_rot, freq_base, vec, st);
+    else if (c->type == B200_KV_Q8_0) rope_rows_k<B200_KV_Q8_0><<<T, ROPE_THR, smem, s>>>(qb, kb, vb, q_out, cs_out, g, p0, rope0, Hq, Hkv, D, n_rot, freq_base, vec, st);
+    else rope_rows_k<B200_KV_Q4_0><<<T, ROPE_THR, smem, s>>>(qb, kb, vb, q_out, cs_out, g, p0, rope0, Hq, Hkv, D, n_rot, freq_base, vec, st);
     count_launch();
     return launch_status(who);
 }
@@ -537,7 +539,12 @@ int b200_attn_prep_rows(const float * qg, const float * k, const float * v, cons
 int b200_rope_append_bf16(const uint16_t * q, const uint16_t * k, const uint16_t * v, float * q_out,
                           const b200_kv_cache * c, int p0, int T, int Hq, int Hkv, int D, int n_rot, float freq_base,
                           void * stream) {
-    return rope_append_launch(q, k, v, q_out, nullptr, c, p0, T, Hq, Hkv, D, n_rot, freq_base, (cudaStream_t) stream, "rope_append_bf16");
+    return rope_append_launch(q, k, v, q_out, nullptr, c, p0, T, Hq, Hkv, D, n_rot, freq_base, (cudaStream_t) stream, "rope_append_bf16", -1);
+}
+int b200_rope_append_bf16_at(const uint16_t * q, const uint16_t * k, const uint16_t * v, float * q_out, const b200_kv_cache * c, int row0,
+                             int rope0, int T, int Hq, int Hkv, int D, int n_rot, float freq_base, void * stream) {
+    if (rope0 < 0) B200_REFUSE(B200_ERR_SHAPE, "rope_append_bf16_at: negative rotary position");
+    return rope_append_launch(q, k, v, q_out, nullptr, c, row0, T, Hq, Hkv, D, n_rot, freq_base, (cudaStream_t) stream, "rope_append_bf16_at", rope0);
 }
 
 int b200_sigmoid_mul(float * x, const float * g, int64_t n, void * stream) {

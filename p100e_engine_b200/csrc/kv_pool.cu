@@ -184,6 +184,15 @@ const int32_t * b200_pool_table_host(const b200_pool * p) { return p ? p->ptab_h
 void * b200_pool_base(const b200_pool * p) { return p ? p->base : nullptr; }
 int b200_pool_local_length(const b200_pool * p, int n_positions) { return p ? local_len(p, n_positions) : 0; }
 
+// raw bytes of the pool -> dst (host or device memory), asynchronous on the stream; for tools that inspect or checkpoint pages
+int b200_pool_read(const b200_pool * p, size_t offset, void * dst, size_t nbytes, void * stream) {
+    if (!p || !dst || offset > p->total || nbytes > p->total - offset) B200_REFUSE(B200_ERR_SHAPE, "pool_read: range outside the pool");
+    if (!on_device(p)) { memcpy(dst, p->base + offset, nbytes); return B200_OK; }
+    const cudaError_t e = cudaMemcpyAsync(dst, p->base + offset, nbytes, cudaMemcpyDefault, (cudaStream_t) stream);
+    if (e != cudaSuccess) { cudaGetLastError(); B200_REFUSE(B200_ERR_CUDA, "pool_read: %s", cudaGetErrorString(e)); }
+    return B200_OK;
+}
+
 // ensure_pages: make global positions [0, n_positions) of the slot addressable on this shard.  New table entries go to the
 // device with one stream-ordered copy from the pinned row (entries already uploaded are never rewritten while in flight).
 int b200_pool_ensure(b200_pool * p, int slot, int n_positions, void * stream) {

@@ -192,6 +192,12 @@ def rope_append_bf16(q, k, v, q_out, c, p0, T, Hq, Hkv, D, n_rot, freq_base, s=N
                                           n_rot, freq_base, _stream(s)) == L.OK
 
 
+def rope_append_bf16_at(q, k, v, q_out, c, row0, rope0, T, Hq, Hkv, D, n_rot, freq_base, s=None):
+    """rope_append_bf16 with separate cache row / rotary position (sequence shards); k = v = None rotates q only"""
+    return L.load().b200_rope_append_bf16_at(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(q_out), C.byref(c.c()), row0, rope0, T, Hq, Hkv, D,
+                                             n_rot, freq_base, _stream(s)) == L.OK
+
+
 def sigmoid_mul(x, g, n, s=None):
     return L.load().b200_sigmoid_mul(L.ptr(x), L.ptr(g), n, _stream(s)) == L.OK
 

@@ -51,6 +51,7 @@ SIGNATURES = {
     "b200_attn_prep": (I, [P, P, P, P, P, P, P, P, KVP, I, I, I, I, I, I, F, F, P, I, I, I, C.POINTER(MropePos)]),
     "b200_attn_prep_rows": (I, [P, P, P, P, P, P, P, P, P, KVP, I, I, I, I, I, F, F, P]),
     "b200_rope_append_bf16": (I, [P, P, P, P, KVP, I, I, I, I, I, I, F, P]),
+    "b200_rope_append_bf16_at": (I, [P, P, P, P, KVP, I, I, I, I, I, I, I, F, P]),
     "b200_attn_decode": (I, [P, KVP, P, I, I, I, F, P]),
     "b200_attn_decode_dev": (I, [P, KVP, P, I, P, I, I, F, P]),
     "b200_attn_decode_rows": (I, [P, KVP, P, I, P, I, F, P]),
@@ -84,6 +85,7 @@ SIGNATURES = {
     "b200_pool_destroy": (None, [P]),
     "b200_pool_bytes": (SZ, [P]),
     "b200_pool_base": (P, [P]),
+    "b200_pool_read": (I, [P, SZ, P, SZ, P]),
     "b200_pool_free_pages": (I, [P]),
     "b200_pool_slot_pages": (I, [P, I]),
     "b200_pool_table_host": (P, [P]),

@@ -117,6 +117,10 @@ class Pool:
     def base(self):
         return self.lib.b200_pool_base(self.h)
 
+    def read(self, offset, dst, nbytes, stream=None):
+        """raw pool bytes -> dst (tensor, array or address; host or device memory), asynchronous on the stream"""
+        return self.lib.b200_pool_read(self.h, offset, L.ptr(dst), nbytes, stream)
+
 
 def session_write(fd, fingerprint, n_past, tokens, pools_slots, states=None, stream=None):
     """one sequence file: header, then every (pool, slot) block in rank order with its opaque state bytes"""

@@ -32,9 +32,19 @@ def test_decode_line_has_the_contract_keys(cuda, lib):
     assert r["bound"] == "hbm" and r["unit"] == "GB/s" and r["peak"] > 0 and r["traffic"] > 0
     assert abs(r["frac"] - r["achieved"] / r["peak"]) < 1e-9
     assert set(("sm_mhz", "sm_max_mhz", "reasons")) <= set(d["clocks"])
+    assert len(d["out_fingerprint"]) == 64 and any(x != 0 for x in d["out_fingerprint"])
+
+
+def test_fingerprint_is_a_function_of_the_seed_only(cuda, lib):
+    a = _run("--workload", "verify8", "--no-cpu-baseline", "--chunk", "512")
+    b = _run("--workload", "verify8", "--no-cpu-baseline", "--chunk", "2048")
+    fa, fb = a["out_fingerprint"], b["out_fingerprint"]
+    scale = max(abs(x) for x in fa)
+    assert scale > 0 and max(abs(x - y) for x, y in zip(fa, fb)) <= 2e-3 * scale
 
 
 def test_prefill_line(cuda, lib):
     d = _run("--workload", "prefill8k", "--no-cpu-baseline")
     assert d["metric"] == "prefill_attn_tflops" and d["unit"] == "TFLOP/s" and d["value"] > 0
     assert d["roofline"]["bound"] == "tensor" and 0 < d["roofline"]["frac"] < 1.5 and d["gpu_launches"] > 0
+    assert d["e2e"]["h2d_bytes_per_step"] > 0 and d["e2e"]["value"] > 0 and d["config"]["workload"] == "prefill8k"
