@@ -70,6 +70,7 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-prefill", action="store_true", help="leave the prefill record out of the decode line")
     ap.add_argument("--no-graph", action="store_true", help="never replay the step from a CUDA graph")
+    ap.add_argument("--breakdown", action="store_true", help="add per-layer times of the step's parts (an extra eager pass)")
     ap.add_argument("--q-len", type=int, default=0, help="override the workload's query rows per slot (1..4)")
     ap.add_argument("--seed", type=int, default=0xB200)
     return ap.parse_args()
@@ -375,7 +376,7 @@ class Workload:
         streams = [torch.cuda.current_stream()] if self.merge is None else self.sub_streams
         for st in streams:
             with torch.cuda.stream(st):
-                assert fast.attn_reserve(slots, q_len, self.max_n, self.max_pages << PSH, hkv, self.chunk)
+                assert fast.attn_reserve(kt, slots, q_len, self.max_n, self.max_pages << PSH, hkv, self.chunk)
         torch.cuda.synchronize()
 
     def sub_cache(self, l, a):
@@ -508,6 +509,56 @@ class Workload:
     def e2e_bytes(self):
         return self.h_in[0].numel() * 4 * self.layers, self.h_out[0].numel() * 4 * self.layers
 
+    def breakdown(self, steps):
+        """per-layer device times of the step's parts from CUDA events on this rank (eager launches, the slots in one batch, no
+        overlap between parts), and the host's time to issue a layer"""
+        torch, fast = self.torch, self.fast
+        names = ["attn_prep", "work list + decode_part_k + chunk merge"]
+        if self.merge is not None:
+            import torch.distributed as dist
+            from p100e_engine_b200 import dist as Dm
+            names += ["all-gather of (O, m, l) in the pair (NCCL)", "merge of the shards + gate"]
+            if not hasattr(self, "bd_merge"):
+                self.bd_merge = Dm.SeqMerge(self.plan, self.rows, self.hq, D, self.dev, self.merge[0].group)
+            mg = self.bd_merge
+        acc = np.zeros(len(names))
+        host = 0.0
+        for it in range(steps + 1):
+            ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)] for _ in range(self.layers)]
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for l in range(self.layers):
+                c = self.caches[l]
+                ev[l][0].record()
+                ok = fast.attn_prep_rows(self.d_qg[l], self.d_k[l], self.d_v[l], self.qn, self.kn, self.rope_pos, self.cache_row, self.q,
+                                         self.gate, c, self.rows, self.hq, self.hkv, D, N_ROT, ROPE_BASE, EPS)
+                ev[l][1].record()
+                if self.merge is None:
+                    ok = ok and fast.attn_decode_slots(self.q, c, self.out, self.gate, self.slots, self.q_len, self.last_key, self.max_n,
+                                                       self.hq, SCALE, self.chunk)
+                    ev[l][2].record()
+                else:
+                    po, pm, pl = mg.views()
+                    ok = ok and fast.attn_decode_slots_partial(self.q, c, po, pm, pl, self.slots, self.q_len, self.last_key, self.max_n,
+                                                               self.hq, SCALE, self.chunk)
+                    ev[l][2].record()
+                    dist.all_gather_into_tensor(mg.recv.view(-1), mg.send, group=mg.group)
+                    ev[l][3].record()
+                    ok = ok and fast.seq_exchange_merge(0, self.plan.n_seq, mg.send, mg.recv, mg.R, D, self.gate, self.out.view(mg.R, D))
+                    ev[l][4].record()
+                assert ok
+            t1 = time.perf_counter()
+            torch.cuda.synchronize()
+            if it == 0:
+                continue      # warm-up (scratch of this stream, the extra merge buffers)
+            host += (t1 - t0) / self.layers
+            for l in range(self.layers):
+                for i in range(len(names)):
+                    acc[i] += ev[l][i].elapsed_time(ev[l][i + 1])
+        per = acc / (steps * self.layers) * 1e3
+        return {"unit": "us per layer", "parts": {n: round(float(v), 2) for n, v in zip(names, per)},
+                "sum": round(float(per.sum()), 2), "host_issue": round(host / steps * 1e6, 2)}
+
     # ---- checks and samples
     def fingerprint(self, world):
         """64 fixed (row, global head, dim) samples of layer 0's gated output, each taken on the rank that owns the head"""
@@ -638,6 +689,7 @@ def run_b200(args):
     if status:
         raise SystemExit("bench.py: a kernel recorded device status %d" % status)
     fingerprint = wl.fingerprint(world)
+    bd = wl.breakdown(max(3, min(args.steps, 10))) if args.breakdown else None
 
     prefill = None
     if args.workload == "whole_box" and not args.no_prefill:
@@ -677,6 +729,8 @@ def run_b200(args):
                               "timing": "CUDA events around each layer's attention call on the launching stream, " +
                                         ("in an eager pass of the same steps (%.3f ms per step; the timed value replays a graph)" % (ms_eager / args.steps)
                                          if graph is not None else "inside the timed region")}})
+    if bd is not None:
+        line["breakdown"] = bd
     if prefill is not None:
         line["prefill"] = prefill
     if not args.no_cpu_baseline:

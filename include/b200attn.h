@@ -151,7 +151,8 @@ int b200_attn_fixed_chunk(int n_ctx);  /* the chunk the entry points above use f
  * valid.  A call that needs more than was reserved gets a new, larger buffer (cudaMalloc, no synchronisation); the old one
  * stays allocated until the process exits, so earlier recorded work never reads freed memory.  Two calls on the same
  * (device, stream) are stream-ordered and may share the buffer; calls on different streams use different buffers. */
-int b200_attn_reserve(int max_slots, int q_len, int max_n, int n_ctx, int Hkv, int chunk_keys, void *stream);
+int b200_attn_reserve(uint32_t kv_type, int max_slots, int q_len, int max_n, int n_ctx, int Hkv, int chunk_keys,
+                      void *stream);
 
 /* Batched decode / verify, any number of slots (new; the reference stops at 8 rows per call, attn.cuh:66).
  * n_slots sequences, q_len (1..4) query rows each; row r = slot * q_len + j sits at pos[r] (device) and sees keys
@@ -159,8 +160,11 @@ int b200_attn_reserve(int max_slots, int q_len, int max_n, int n_ctx, int Hkv, i
  * pt + rtab[slot * q_len] (rtab == NULL: one table for all).  The q_len rows of a slot share one pass over its KV.
  * gate != NULL: out = attn * sigmoid(gate) fused into the split merge (ew_quant(EW_SIGMOID_MUL), fused.cu:479-496;
  * k::sigmoid_mul, src/kernels.cu:85-93).  max_n: upper bound of pos[r] + 1 over the call (sizes the grid).
- * chunk_keys: keys per split (multiple of 64); 0 = the library default, -1 = chosen from the batch size.
- * Each row's result depends only on its own keys and on chunk_keys, never on the other rows of the call. */
+ * chunk_keys: keys per split (multiple of 64); 0 = the library default (a function of the cache's capacity); -1 = an even
+ * split of the whole batch: the batch's 64-key tiles, slot after slot, are cut into one contiguous run per resident CTA, so
+ * ragged contexts load every SM equally (up to 2048 slots; larger batches take a chunk chosen from the batch size).
+ * With chunk_keys >= 0 each row's result depends only on its own keys and on the chunk, never on the other rows of the call
+ * (bitwise); with -1 the split points depend on the batch, so results of different batches agree to rounding only. */
 int b200_attn_decode_slots(const float *q, const b200_kv_cache *c, float *out, const float *gate, int n_slots,
                            int q_len, const int32_t *pos, int max_n, int Hq, float scale, int chunk_keys, void *stream);
 /* b200_attn_decode_slots for callers that cannot allocate device memory (no counterpart in the reference, whose decode

@@ -21,7 +21,7 @@
 // a row's result is a function of its own keys and of chunk_keys only (row t of a T-row call == the 1-row call).
 //
 // Reference counterpart: dec2_k / attn_decode2 (src/fast/attn_dec2.cu:210-530), fp32 FFMA on sm_60.
-#include "common.cuh"
+#include "umma.cuh"
 
 #include <dlfcn.h>
 #include <cuda.h>   // CUtensorMap and its enums only: the encoder is looked up at run time, nothing links against libcuda
@@ -58,6 +58,16 @@ template <uint32_t KT> struct traits {
     static constexpr int SLOT = TILE * SROW;                        // one ring slot: the K rows or the V rows of a tile
     static constexpr bool SCALED = KT != B200_KV_F16;
 };
+// Verify calls on quantised caches (two or three row tiles) keep 32 or 48 output accumulators per thread, which are idle
+// during Q K^T and the softmax: there they are parked in tensor memory (tcgen05.st / tcgen05.ld, this warp's own 32 lanes),
+// so the compiler has those registers for loads in flight.  PARK_COLS columns are allocated per CTA.
+#ifndef DEC_PARK
+#define DEC_PARK 1
+#endif
+
+template <uint32_t KT, int NT> constexpr bool parks() { return DEC_PARK && KT != B200_KV_F16 && NT >= 2; }
+constexpr uint32_t PARK_COLS = 64;
+
 // f16 slots hold four sub-tiles [64 rows][128 B] (dims 64 c .. 64 c + 63) with the 128-byte swizzle of the TMA unit: the
 // 16-byte chunk j of a sub-tile row sits at chunk j ^ (row & 7), which keeps 16-byte and ldmatrix accesses of eight
 // different rows on different banks.  chunk16 = 16-byte chunk of the 512-byte head row.
@@ -95,6 +105,11 @@ struct dec_args {
     int tiled;                            // set by the launcher: whole tiles are fetched through the tensor maps
     const int2 * units;                   // work list written by decode_plan_k: (slot, chunk), longest first; nullptr = the
     const int * n_units;                  // grid itself enumerates (slot, chunk) and units past a slot's end exit
+    // even split (decode_split_k): the batch's 64-key tiles, slot after slot, are cut into one contiguous run per CTA
+    const int4 * segs;                    // (slot, first key, end key, 0) in CTA order; a run that crosses a slot boundary has several
+    const int * cta_seg;                  // [n_cta + 1] first segment of each CTA
+    const int2 * slot_seg;                // [n_slots] (first segment, segments) of each slot
+    const int * n_cta;                    // CTAs (per kv head) that hold work
 };
 
 // keys of a slot that the call may touch: 1 + its largest row position, held to the caller's max_n (the grid and the
@@ -133,23 +148,17 @@ __device__ __forceinline__ void tma_box4(void * dst, const CUtensorMap * map, in
                  ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(w), "r"(smem_u32(bar)) : "memory");
 }
 
+// One unit of work: the keys k_lo .. k_cap-1 (as far as the slot has them) of one slot and kv head, all its query rows;
+// writes the unnormalised partial (O, m, l) number `unit`.  Called by all threads of the CTA.  A CTA that runs several units
+// keeps its ring of copy slots, their barriers and the arrival counters going from one unit to the next: tiles_before is the
+// number of tiles its earlier units walked (two ring items each); the function returns this unit's tile count.
+// t_base: tensor-memory base of the parked accumulators.
 template <uint32_t KT, int NT>
-__global__ void __launch_bounds__(NTHR, ctas_per_sm<KT, NT>())
-decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV) {
+__device__ __forceinline__ int decode_unit(const dec_args & a, const int nslot, const CUtensorMap & mapK, const CUtensorMap & mapV,
+                                           unsigned char * smem, const int hk, const int slot, const int k_lo, const int k_cap,
+                                           const size_t unit, const int tiles_before, const uint32_t t_base) {
     using TR = traits<KT>;
     constexpr int HB = TR::HB, SROW = TR::SROW;
-    extern __shared__ __align__(1024) unsigned char smem[];
-    // blockIdx.x = unit * Hkv + kv head: the heads of one (slot, chunk) are neighbours in launch order, so the four
-    // head rows of a position are fetched close together in time
-    const int hk = (int) (blockIdx.x % (unsigned) a.g.Hkv), ui = (int) (blockIdx.x / (unsigned) a.g.Hkv);
-    int slot, chunk;
-    if (a.units) {
-        if (ui >= *a.n_units) return;
-        const int2 u = a.units[ui];
-        slot = u.x; chunk = u.y;
-    } else {
-        slot = ui / a.max_chunks; chunk = ui - slot * a.max_chunks;
-    }
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, g = lane >> 2, t = lane & 3;
     const int R = a.q_len * GQA;
 
@@ -160,10 +169,11 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
         const int lim = key_limit(a);
         if (n_slot > lim) { if (tid == 0) atomicOr(a.status, ST_BAD_POS); n_slot = lim; }
     }
-    const int k_lo = chunk * a.CH;
-    if (k_lo >= n_slot) return;
-    const int k_hi = min(k_lo + a.CH, n_slot);
+    if (k_lo >= n_slot) return 0;
+    const int k_hi = min(k_cap, n_slot);
     const int ntiles = (k_hi - k_lo + TILE - 1) / TILE;
+    const int ring0 = (2 * tiles_before) % nslot;                       // ring slot of this unit's first item
+    const uint32_t ring0_par = (uint32_t) ((2 * tiles_before) / nslot) & 1u;   // and the parity of that slot's use count
 
     // shared memory carve-up
     uint64_t * full = reinterpret_cast<uint64_t *>(smem);                    // [nslot]
@@ -233,16 +243,14 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
         if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&full[s])) : "memory");
     };
     // warp 0 starts the first copies before anything else, so that they fly while Q is staged
-    if (w == 0) {
-        if (lane == 0) {
-            for (int s = 0; s < nslot; ++s) mbar_init(&full[s], 1);
-            mbar_fence_init();
-            done[0] = done[1] = 0;
-            flag[0] = flag[1] = flag[2] = 0;
+    if (w == 0) {   // every slot is free at the start of a unit: all items of the earlier units have been consumed
+        int s = ring0;
+        for (int q0 = 0; q0 < nslot; ++q0) {
+            issue(q0, s, true);
+            if (++s == nslot) s = 0;
         }
-        __syncwarp();
-        for (int q0 = 0; q0 < nslot; ++q0) issue(q0, q0, true);
     }
+    constexpr bool PARK = parks<KT, NT>();
     if (pg_staged)
         for (int j = tid; j <= ((k_hi - 1) >> a.g.psh) - pg0; j += NTHR) pgs[j] = tab[pg0 + j];
     // Q rows -> shared memory as f16, scaled; row r = j * 6 + hh (verify row j, head hh of the group).  For the quantised
@@ -313,6 +321,34 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
         for (int i = 0; i < NT; ++i)
 #pragma unroll
             for (int e = 0; e < 4; ++e) O[mt][i][e] = 0.0f;
+    // parked accumulators: 16 * NT columns of this warp's 32 tensor-memory lanes
+    uint32_t t_O = 0;
+    auto park = [&]() {
+        const float * o = &O[0][0][0];
+#pragma unroll
+        for (int c = 0; c < NT; ++c) {
+            uint32_t r[16];
+#pragma unroll
+            for (int e = 0; e < 16; ++e) r[e] = __float_as_uint(o[16 * c + e]);
+            umma::tmem_st16(t_O + 16 * c, r);
+        }
+        umma::tmem_st_wait();
+    };
+    auto unpark = [&]() {
+        float * o = &O[0][0][0];
+#pragma unroll
+        for (int c = 0; c < NT; ++c) {
+            uint32_t r[16];
+            umma::tmem_ld16(t_O + 16 * c, r);
+#pragma unroll
+            for (int e = 0; e < 16; ++e) o[16 * c + e] = __uint_as_float(r[e]);
+        }
+        umma::tmem_ld_wait();
+    };
+    if constexpr (PARK) {
+        t_O = t_base + ((uint32_t) (32 * w) << 16);
+        park();
+    }
 
     const int kA = 16 * w + key_perm<KT>(g), kB = kA + 8;   // this lane's two keys (tile-relative) in the QK phase
     int rmin = 0x7fffffff;   // the mask is only evaluated in tiles that reach past some row's last key or the chunk's end
@@ -321,8 +357,9 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
 
     // ring position of the tile's K item (2 it) and V item (2 it + 1): slot index and the parity of its use count
     int last_v = 0, sv_prev = 0;
-    int sk = 0, sv = 1 % nslot;
-    uint32_t phk = 0, phv = nslot == 1 ? 1u : 0u;
+    int sk = ring0, sv = ring0 + 1;
+    uint32_t phk = ring0_par, phv = ring0_par;
+    if (sv >= nslot) { sv -= nslot; phv ^= 1u; }
     for (int it = 0; it < ntiles; ++it) {
         const unsigned char * Ks = stg + (size_t) sk * TR::SLOT;
         const unsigned char * Vs = stg + (size_t) sv * TR::SLOT;
@@ -430,14 +467,14 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
         for (int i = 0; i < NT; ++i)
 #pragma unroll
             for (int e = 0; e < 2; ++e) grow = grow || fmaxf(S[i][e], S[i][2 + e]) > m_run[i][e] + REF_GAP;
-        const int ph = it % 3;   // three flags in turn: the one of the next tile is cleared two barriers after its last reader
+        const int ph = (tiles_before + it) % 3;   // three flags in turn: the one of the next tile is cleared two barriers after its last reader
         if (__any_sync(0xffffffffu, grow) && lane == 0) flag[ph] = 1;
         if (tid == 0) flag[ph == 2 ? 0 : ph + 1] = 0;
         refill_if_last(last_k, 2 * it, sk_now);
         // P and the V scales of this tile replace those of the previous tile: every warp must be done with its P V
         if (it > 0) {
             int spins = 0;
-            while (*reinterpret_cast<volatile int *>(&done[1]) < NWARP * it)
+            while (*reinterpret_cast<volatile int *>(&done[1]) < NWARP * (tiles_before + it))
                 if (++spins > (1 << 24)) { atomicOr(a.status, ST_WAIT_TIMEOUT); break; }
         }
         float lsum[NT][2];
@@ -467,6 +504,7 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
             }
         }
         __syncthreads();   // P, the V scales, the warps' maxima and the flag are visible
+        if constexpr (PARK) unpark();
         if (flag[ph]) {
             // the warps' row maxima over their 16 keys, exchanged through shared memory
 #pragma unroll
@@ -581,7 +619,9 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
         }
         last_v = arrive(1);
         sv_prev = sv_now;
+        if constexpr (PARK) park();
     }
+    if constexpr (PARK) unpark();
 
     // ---------------- write the unit's partial ----------------
     // l: sum over the lanes that share this row pair (same t), then over the warps
@@ -596,7 +636,6 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
             if (g == 0) wl[w * NT * 8 + 8 * i + 2 * t + e] = l;
         }
     __syncthreads();
-    const size_t unit = ((size_t) slot * a.g.Hkv + hk) * a.max_chunks + chunk;
     if (w == 0 && g == 0) {
 #pragma unroll
         for (int i = 0; i < NT; ++i)
@@ -635,6 +674,77 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
                 }
             }
         }
+    return ntiles;
+}
+
+// The kernel: one unit per CTA (the grid enumerates (slot, chunk), directly or through the work list), or, with the even
+// split, every segment of the CTA's run one after the other.
+template <uint32_t KT, int NT>
+__global__ void __launch_bounds__(NTHR, ctas_per_sm<KT, NT>())
+decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    // blockIdx.x = unit * Hkv + kv head: the heads of one (slot, key range) are neighbours in launch order, so the four
+    // head rows of a position are fetched close together in time
+    const int hk = (int) (blockIdx.x % (unsigned) a.g.Hkv), ui = (int) (blockIdx.x / (unsigned) a.g.Hkv);
+    int s0 = 0, s1 = 1, slot = 0, k_lo = 0, k_cap = 0;
+    size_t unit = 0;
+    if (a.segs) {
+        if (ui >= *a.n_cta) return;
+        s0 = a.cta_seg[ui]; s1 = a.cta_seg[ui + 1];
+        if (s0 >= s1) return;
+    } else {
+        int chunk;
+        if (a.units) {
+            if (ui >= *a.n_units) return;
+            const int2 u = a.units[ui];
+            slot = u.x; chunk = u.y;
+        } else {
+            slot = ui / a.max_chunks; chunk = ui - slot * a.max_chunks;
+        }
+        int n = 0;
+        for (int j = 0; j < a.q_len; ++j) n = max(n, row_pos(a, slot, j) + 1);
+        k_lo = chunk * a.CH;
+        if (k_lo >= min(n, key_limit(a))) return;   // the chunk lies past the slot's keys
+        k_cap = k_lo + a.CH;
+        unit = ((size_t) slot * a.g.Hkv + hk) * a.max_chunks + chunk;
+    }
+    // barriers of the copy ring, arrival counters and flags: made once per CTA
+    if (threadIdx.x == 0) {
+        uint64_t * full = reinterpret_cast<uint64_t *>(smem);
+        for (int s = 0; s < nslot; ++s) mbar_init(&full[s], 1);
+        mbar_fence_init();
+        int * cnt = reinterpret_cast<int *>(smem + 96);   // done[2], flag[3]
+        cnt[0] = cnt[1] = cnt[2] = cnt[3] = cnt[4] = 0;
+    }
+    uint32_t t_base = 0;
+    uint32_t * t_slot = reinterpret_cast<uint32_t *>(smem + 120);
+    if constexpr (parks<KT, NT>()) {
+        if (threadIdx.x >= 32 && threadIdx.x < 64) umma::tmem_alloc(t_slot, PARK_COLS);
+        umma::fence_before_sync();
+    }
+    __syncthreads();
+    if constexpr (parks<KT, NT>()) {
+        umma::fence_after_sync();
+        t_base = *t_slot;
+    }
+    int tiles = 0;
+    for (int sg = s0; sg < s1; ++sg) {
+        if (a.segs) {
+            const int4 e = a.segs[sg];
+            slot = e.x; k_lo = e.y; k_cap = e.z;
+            unit = (size_t) sg * a.g.Hkv + hk;
+        }
+        if (sg > s0) __syncthreads();   // the previous segment's shared memory is no longer read
+        tiles += decode_unit<KT, NT>(a, nslot, mapK, mapV, smem, hk, slot, k_lo, k_cap, unit, tiles, t_base);
+    }
+    if constexpr (parks<KT, NT>()) {
+        umma::fence_before_sync();
+        __syncthreads();
+        if (threadIdx.x >= 32 && threadIdx.x < 64) {
+            umma::fence_after_sync();
+            umma::tmem_dealloc(t_base, PARK_COLS);
+        }
+    }
 }
 
 // Merge a row's chunk partials.  grid (rows, Hq), 256 threads = 4 groups of 64 (one float4 of the head each): group w sums the
@@ -652,18 +762,28 @@ __global__ void __launch_bounds__(64 * MERGE_GROUPS) decode_merge_k(const dec_ar
     const int h = blockIdx.y, row = blockIdx.x, slot = row / a.q_len, j = row - slot * a.q_len;
     const int hk = h / GQA, hh = h - hk * GQA, r = j * GQA + hh, R = a.q_len * GQA;
     const int pos = min(row_pos(a, slot, j), key_limit(a) - 1);   // a row past the limit merges the chunks that exist
-    const int nch = pos < 0 ? 0 : pos / a.CH + 1;
-    const size_t unit0 = ((size_t) slot * a.g.Hkv + hk) * a.max_chunks;
+    // partials of the row's kv head: consecutive units of stride ustr from unit0 (a segment the row does not reach holds m = -inf)
+    int nch;
+    size_t unit0, ustr;
+    if (a.segs) {
+        const int2 sg = a.slot_seg[slot];
+        nch = pos < 0 ? 0 : sg.y;
+        unit0 = (size_t) sg.x * a.g.Hkv + hk; ustr = a.g.Hkv;
+    } else {
+        nch = pos < 0 ? 0 : pos / a.CH + 1;
+        unit0 = ((size_t) slot * a.g.Hkv + hk) * a.max_chunks; ustr = 1;
+    }
     float M = B200_NEG_INF;
-    for (int c = 0; c < nch; ++c) M = fmaxf(M, a.pm[(unit0 + c) * R + r]);
+    for (int c = 0; c < nch; ++c) M = fmaxf(M, a.pm[(unit0 + c * ustr) * R + r]);
     float den = 0.0f;
     float4 num = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll 4
     for (int c = grp; c < nch; c += MERGE_GROUPS) {   // no early continue: the loads of several chunks are in flight together
-        const float ms = a.pm[(unit0 + c) * R + r];
+        const size_t u = unit0 + c * ustr;
+        const float ms = a.pm[u * R + r];
         const float f = ms == B200_NEG_INF ? 0.0f : ex2f(ms - M);   // a chunk the row did not see holds zeros: adds nothing
-        den = fmaf(f, a.pl[(unit0 + c) * R + r], den);
-        const float4 o = reinterpret_cast<const float4 *>(a.po + ((unit0 + c) * R + r) * DH)[lane4];
+        den = fmaf(f, a.pl[u * R + r], den);
+        const float4 o = reinterpret_cast<const float4 *>(a.po + (u * R + r) * DH)[lane4];
         num.x = fmaf(f, o.x, num.x); num.y = fmaf(f, o.y, num.y); num.z = fmaf(f, o.z, num.z); num.w = fmaf(f, o.w, num.w);
     }
     if (grp > 0) {
@@ -779,6 +899,98 @@ __global__ void __launch_bounds__(PLAN_THR) decode_plan_k(const dec_args a, int2
             for (int c = 0; c < nfull; ++c) units[base + c] = make_int2(s, c);
         }
         if (tail) units[atomicAdd(&hist[bucket_of(tail)], 1)] = make_int2(s, nfull);
+    }
+}
+
+// Even split of a batch over the resident CTAs (used when the chunk is chosen from the batch).  The 64-key tiles of all
+// slots, slot after slot, form one sequence per kv head; CTA c of n_cta takes tiles [c W / n_cta, (c + 1) W / n_cta), so
+// every CTA has the same work to within one tile however ragged the contexts are, and all CTAs fit the machine at once.  A
+// run that crosses slot boundaries becomes several segments; each segment yields one partial.  n_cta = min(max_cta, W /
+// SPLIT_MIN_TILES) keeps runs from getting so short that start-up and the merge dominate.  One block; n_slots <= SPLIT_MAX_SLOTS.
+constexpr int SPLIT_THR = 1024, SPLIT_MAX_SLOTS = 2048, SPLIT_MAX_CTA = 1024, SPLIT_MIN_TILES = 4;
+__global__ void __launch_bounds__(SPLIT_THR) decode_split_k(const dec_args a, int max_cta, int4 * __restrict__ segs, int * __restrict__ cta_seg,
+                                                            int2 * __restrict__ slot_seg, int * __restrict__ n_cta_out) {
+    __shared__ int pre[SPLIT_MAX_SLOTS + 1];     // tiles before slot s
+    __shared__ int cseg[SPLIT_MAX_CTA + 1];      // segments before CTA c
+    __shared__ int first_slot[SPLIT_MAX_CTA];
+    const int tid = threadIdx.x, lim = key_limit(a);
+    auto slot_keys = [&](int s) {
+        int n = 0;
+        for (int j = 0; j < a.q_len; ++j) n = max(n, row_pos(a, s, j) + 1);
+        return min(n, lim);
+    };
+    for (int s = tid; s < a.n_slots; s += SPLIT_THR) pre[s + 1] = (slot_keys(s) + TILE - 1) / TILE;
+    if (tid == 0) pre[0] = 0;
+    __syncthreads();
+    if (tid < 32) {   // inclusive scan of pre[1..n_slots], 32 entries at a time with a running carry
+        int carry = 0;
+        for (int base = 1; base <= a.n_slots; base += 32) {
+            const int i = base + tid;
+            int v = i <= a.n_slots ? pre[i] : 0;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { const int u = __shfl_up_sync(0xffffffffu, v, o); if (tid >= o) v += u; }
+            if (i <= a.n_slots) pre[i] = v + carry;
+            carry += __shfl_sync(0xffffffffu, v, 31);
+        }
+    }
+    __syncthreads();
+    const long long W = pre[a.n_slots];
+    const int n_cta = (int) max(1LL, min((long long) min(max_cta, SPLIT_MAX_CTA), W / SPLIT_MIN_TILES));
+    auto cut = [&](int c) { return (int) (W * c / n_cta); };
+    // segments per CTA: the slots its run intersects
+    int my_first = 0, my_cnt = 0;
+    if (tid < n_cta) {
+        const int lo = cut(tid), hi = cut(tid + 1);
+        if (hi > lo) {
+            int l = 0, r = a.n_slots;               // last slot with pre[s] <= lo
+            while (r - l > 1) { const int m = (l + r) >> 1; if (pre[m] <= lo) l = m; else r = m; }
+            while (pre[l + 1] <= lo) ++l;           // skip empty slots
+            my_first = l;
+            int e = l;
+            while (e < a.n_slots && pre[e] < hi) { if (pre[e + 1] > pre[e] && pre[e + 1] > lo) ++my_cnt; ++e; }
+        }
+        first_slot[tid] = my_first;
+        cseg[tid + 1] = my_cnt;
+    }
+    if (tid == 0) cseg[0] = 0;
+    __syncthreads();
+    if (tid < 32) {
+        int carry = 0;
+        for (int base = 1; base <= n_cta; base += 32) {
+            const int i = base + tid;
+            int v = i <= n_cta ? cseg[i] : 0;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { const int u = __shfl_up_sync(0xffffffffu, v, o); if (tid >= o) v += u; }
+            if (i <= n_cta) cseg[i] = v + carry;
+            carry += __shfl_sync(0xffffffffu, v, 31);
+        }
+    }
+    __syncthreads();
+    if (tid <= n_cta) cta_seg[tid] = cseg[tid];
+    if (tid == 0) *n_cta_out = W > 0 ? n_cta : 0;
+    if (tid < n_cta && my_cnt > 0) {
+        const int lo = cut(tid), hi = cut(tid + 1);
+        int o = cseg[tid];
+        for (int s = my_first; s < a.n_slots && pre[s] < hi; ++s) {
+            if (pre[s + 1] <= pre[s] || pre[s + 1] <= lo) continue;
+            const int t0 = max(lo, pre[s]) - pre[s], t1 = min(hi, pre[s + 1]) - pre[s];
+            segs[o++] = make_int4(s, t0 * TILE, t1 * TILE, 0);
+        }
+    }
+    // the segments of a slot are consecutive: from the CTA that holds its first tile to the one that holds its last
+    for (int s = tid; s < a.n_slots; s += SPLIT_THR) {
+        if (pre[s + 1] <= pre[s]) { slot_seg[s] = make_int2(0, 0); continue; }
+        auto cta_of = [&](int tile) {
+            int c = (int) min((long long) n_cta - 1, ((long long) tile * n_cta) / max(W, 1LL));
+            while (c > 0 && cut(c) > tile) --c;
+            while (c + 1 < n_cta && cut(c + 1) <= tile) ++c;
+            return c;
+        };
+        const int c0 = cta_of(pre[s]), c1 = cta_of(pre[s + 1] - 1);
+        // inside CTA c0 the slot's segment comes after those of the non-empty slots first_slot[c0] .. s-1
+        int before = 0;
+        for (int z = first_slot[c0]; z < s; ++z) if (pre[z + 1] > pre[z] && pre[z + 1] > cut(c0)) ++before;
+        slot_seg[s] = make_int2(cseg[c0] + before, c1 - c0 + 1);
     }
 }
 
@@ -959,6 +1171,20 @@ int sm_count() {
     return sms;
 }
 
+// CTAs of decode_part_k<type, row tiles> that fit an SM at once (the same rule as launch_part)
+template <uint32_t KT, int NT> int ctas_fitting() {
+    int ctas = ctas_per_sm<KT, NT>();
+    while (ctas > 1 && (size_t) ctas * (smem_bytes<KT, NT>(2) + 1024) > (size_t) 227 * 1024) --ctas;
+    return ctas;
+}
+template <uint32_t KT> int ctas_fitting_nt(int nt) { return nt == 1 ? ctas_fitting<KT, 1>() : nt == 2 ? ctas_fitting<KT, 2>() : ctas_fitting<KT, 3>(); }
+int resident_ctas(uint32_t type, int q_len) {
+    const int nt = (q_len * GQA + 7) / 8;
+    const int per_sm = type == B200_KV_F16 ? ctas_fitting_nt<B200_KV_F16>(nt) : type == B200_KV_Q8_0 ? ctas_fitting_nt<B200_KV_Q8_0>(nt)
+                                                                                                 : ctas_fitting_nt<B200_KV_Q4_0>(nt);
+    return per_sm * sm_count();
+}
+
 int auto_chunk(long long total_keys, int Hkv) {
     // enough units for several waves over the SMs, chunks between 256 and 4096 keys
     const long long units = 8LL * sm_count();
@@ -969,13 +1195,30 @@ int auto_chunk(long long total_keys, int Hkv) {
 }
 
 // geometry of a call: chunk, chunks per slot, partial floats, work-list ints
-struct dec_geom { int CH, max_chunks, R; size_t units, part_floats, list_ints; bool planned; };
+//   split   (chunk chosen from the batch, up to SPLIT_MAX_SLOTS slots): one contiguous run of tiles per resident CTA
+//   planned (fixed chunk, more units than a wave): the grid's units ordered longest first through a work list
+//   else    the grid enumerates (slot, chunk)
+struct dec_geom { int CH, max_chunks, R, max_cta; size_t units, part_floats, list_ints; bool planned, split; };
 
-bool decode_geometry(dec_geom & g, int n_slots, int q_len, int max_n, int n_ctx, int Hkv, int chunk_keys) {
+bool decode_geometry(dec_geom & g, uint32_t type, int n_slots, int q_len, int max_n, int n_ctx, int Hkv, int chunk_keys) {
     if (max_n < 1) max_n = 1;
+    g.R = q_len * GQA;
+    g.split = chunk_keys < 0 && n_slots > 1 && n_slots <= SPLIT_MAX_SLOTS;   // one sequence is even as it is: no plan launch
+    g.planned = false;
+    g.max_cta = 0;
+    if (g.split) {
+        g.CH = TILE;
+        g.max_chunks = (max_n + TILE - 1) / TILE;
+        g.max_cta = std::max(1, std::min(SPLIT_MAX_CTA, resident_ctas(type, q_len) / Hkv));
+        const size_t nseg = (size_t) g.max_cta + n_slots;
+        g.units = nseg * Hkv;
+        g.part_floats = g.units * g.R * (DH + 2);
+        g.list_ints = 4 * nseg + 2 * (size_t) n_slots + g.max_cta + 2;
+        g.list_ints = (g.list_ints + 3) & ~(size_t) 3;
+        return true;
+    }
     g.CH = chunk_keys > 0 ? round_tile(chunk_keys) : chunk_keys < 0 ? auto_chunk((long long) n_slots * max_n / 2, Hkv) : fixed_chunk(n_ctx);
     g.max_chunks = (max_n + g.CH - 1) / g.CH;
-    g.R = q_len * GQA;
     g.units = (size_t) n_slots * Hkv * g.max_chunks;
     if (g.units >= ((size_t) 1 << 31) || (size_t) n_slots * g.max_chunks >= ((size_t) 1 << 30)) return false;
     g.part_floats = g.units * g.R * (DH + 2);
@@ -1013,15 +1256,27 @@ int decode_launch(const float * q, const b200_kv_cache * c, const merge_out & mo
     a.CH = gm.CH; a.max_chunks = gm.max_chunks; a.status = st;
     a.n_ctx = c->n_ctx; a.tiled = 0;
     a.units = nullptr; a.n_units = nullptr;
+    a.segs = nullptr; a.cta_seg = nullptr; a.slot_seg = nullptr; a.n_cta = nullptr;
     int launches = 2;
-    if (gm.planned) {
+    unsigned blocks = (unsigned) gm.units;
+    if (gm.split) {
+        int * list = reinterpret_cast<int *>(scr + gm.part_floats);
+        const size_t nseg = (size_t) gm.max_cta + n_slots;
+        int4 * segs = reinterpret_cast<int4 *>(list);
+        int2 * slot_seg = reinterpret_cast<int2 *>(list + 4 * nseg);
+        int * cta_seg = list + 4 * nseg + 2 * (size_t) n_slots;
+        int * n_cta = cta_seg + gm.max_cta + 1;
+        a.segs = segs; a.cta_seg = cta_seg; a.slot_seg = slot_seg; a.n_cta = n_cta;
+        decode_split_k<<<1, SPLIT_THR, 0, s>>>(a, gm.max_cta, segs, cta_seg, slot_seg, n_cta);
+        ++launches;
+        blocks = (unsigned) gm.max_cta * (unsigned) c->Hkv;
+    } else if (gm.planned) {
         int * list = reinterpret_cast<int *>(scr + gm.part_floats);
         a.n_units = list;
         a.units = reinterpret_cast<const int2 *>(list + 4);
         decode_plan_k<<<1, PLAN_THR, 0, s>>>(a, reinterpret_cast<int2 *>(list + 4), list);
         ++launches;
     }
-    const unsigned blocks = (unsigned) gm.units;
     int rc;
     if (c->type == B200_KV_F16) rc = launch_part_nt<B200_KV_F16>(a, blocks, s);
     else if (c->type == B200_KV_Q8_0) rc = launch_part_nt<B200_KV_Q8_0>(a, blocks, s);
@@ -1043,7 +1298,7 @@ int decode_impl(const float * q, const b200_kv_cache * c, const merge_out & mo, 
     if (chk != B200_OK) return chk;
     if (mo.qbuf && (!mo.out || ((uintptr_t) mo.qbuf & 3))) B200_REFUSE(B200_ERR_SHAPE, "%s: the a16 buffer needs out and 4-byte alignment", who);
     dec_geom gm;
-    if (!decode_geometry(gm, n_slots, q_len, max_n, c->n_ctx, c->Hkv, chunk_keys)) B200_REFUSE(B200_ERR_SHAPE, "%s: too many chunks", who);
+    if (!decode_geometry(gm, c->type, n_slots, q_len, max_n, c->n_ctx, c->Hkv, chunk_keys)) B200_REFUSE(B200_ERR_SHAPE, "%s: too many chunks", who);
     const size_t need = gm.part_floats + gm.list_ints;
     float * scr = scratch_for(s, need, hint_floats);
     if (!scr) B200_REFUSE(B200_ERR_ALLOC, "%s: split scratch (%zu floats) could not be allocated", who, need);
@@ -1095,7 +1350,7 @@ int decode_noalloc_impl(const float * q, const b200_kv_cache * c, float * out, c
     const int chk = decode_check(q, c, out, gate, n_slots, q_len, Hq, who);
     if (chk != B200_OK) return chk;
     dec_geom gm;
-    const bool ok = decode_geometry(gm, n_slots, q_len, max_n, c->n_ctx, c->Hkv, chunk_keys);
+    const bool ok = decode_geometry(gm, c->type, n_slots, q_len, max_n, c->n_ctx, c->Hkv, chunk_keys);
     const size_t need = ok ? gm.part_floats + gm.list_ints : 0;
     if (!ok || need > NOALLOC_FLOATS)
         B200_REFUSE(B200_ERR_SCRATCH, "%s: %zu bytes of split partials needed (slots %d x kv heads %d x chunks %d x rows %d), the built-in array holds %zu; "
@@ -1147,14 +1402,15 @@ int b200_attn_dec2_reload_env(void) {
     return (g_chunk != before || g_chunk_from_env != before_env) ? 1 : 0;
 }
 
-int b200_attn_reserve(int max_slots, int q_len, int max_n, int n_ctx, int Hkv, int chunk_keys, void * stream) {
-    if (max_slots < 1 || max_slots > 65535 || q_len < 1 || q_len > B200_MAX_QLEN || max_n < 1 || Hkv < 1)
+int b200_attn_reserve(uint32_t kv_type, int max_slots, int q_len, int max_n, int n_ctx, int Hkv, int chunk_keys, void * stream) {
+    if (max_slots < 1 || max_slots > 65535 || q_len < 1 || q_len > B200_MAX_QLEN || max_n < 1 || Hkv < 1 ||
+        (kv_type != B200_KV_F16 && kv_type != B200_KV_Q8_0 && kv_type != B200_KV_Q4_0))
         B200_REFUSE(B200_ERR_SHAPE, "attn_reserve: unsupported arguments");
     dec_geom gm;
-    if (!decode_geometry(gm, max_slots, q_len, max_n, n_ctx > 0 ? n_ctx : max_n, Hkv, chunk_keys)) B200_REFUSE(B200_ERR_SHAPE, "attn_reserve: too many chunks");
-    size_t need = gm.part_floats + 2 * (size_t) max_slots * gm.max_chunks + 4;
-    if (chunk_keys < 0) {
-        // a chunk chosen from the batch: smaller batches take smaller chunks; their unit count stays under this bound
+    if (!decode_geometry(gm, kv_type, max_slots, q_len, max_n, n_ctx > 0 ? n_ctx : max_n, Hkv, chunk_keys)) B200_REFUSE(B200_ERR_SHAPE, "attn_reserve: too many chunks");
+    size_t need = gm.part_floats + std::max(gm.list_ints, 2 * (size_t) max_slots * gm.max_chunks + 4);
+    if (chunk_keys < 0 && !gm.split) {
+        // a fixed chunk chosen from the batch: smaller batches take smaller chunks; their unit count stays under this bound
         const size_t u = 2 * 8 * (size_t) sm_count() + (size_t) max_slots * Hkv;
         need = std::max(need, u * q_len * GQA * (DH + 2) + 2 * u + 4);
     }
@@ -1174,7 +1430,7 @@ int b200_attn_decode2(const float * q, const b200_kv_cache * c, float * out, int
     size_t hint = 0;
     if (c && c->Hkv > 0) {
         dec_geom gm;
-        if (decode_geometry(gm, B200_ATTN_MAX_ROWS, 1, n_ctx, n_ctx, c->Hkv, 0)) hint = gm.part_floats + gm.list_ints;
+        if (decode_geometry(gm, c->type, B200_ATTN_MAX_ROWS, 1, n_ctx, n_ctx, c->Hkv, 0)) hint = gm.part_floats + gm.list_ints;
     }
     const merge_out mo = {out, nullptr, nullptr, nullptr, nullptr, nullptr};
     // rows of one sequence at consecutive positions share the pass over its KV (up to 4 rows per slot)
@@ -1197,7 +1453,7 @@ int b200_attn_decode_dev(const float * q, const b200_kv_cache * c, float * out, 
     size_t hint = 0;
     if (c && c->Hkv > 0) {
         dec_geom gm;
-        if (decode_geometry(gm, B200_ATTN_MAX_ROWS, 1, n_ctx, n_ctx, c->Hkv, 0)) hint = gm.part_floats + gm.list_ints;
+        if (decode_geometry(gm, c->type, B200_ATTN_MAX_ROWS, 1, n_ctx, n_ctx, c->Hkv, 0)) hint = gm.part_floats + gm.list_ints;
     }
     const merge_out mo = {out, nullptr, nullptr, nullptr, nullptr, nullptr};
     if (T <= B200_MAX_QLEN)

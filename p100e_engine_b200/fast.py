@@ -103,8 +103,8 @@ def attn_decode_slots_noalloc(q, c, out, gate, n_slots, q_len, pos, max_n, Hq, s
                                                    max_n, Hq, scale, chunk_keys, _stream(s))
 
 
-def attn_reserve(max_slots, q_len, max_n, n_ctx, Hkv, chunk_keys=0, s=None):
-    return L.load().b200_attn_reserve(max_slots, q_len, max_n, n_ctx, Hkv, chunk_keys, _stream(s)) == L.OK
+def attn_reserve(kv_type, max_slots, q_len, max_n, n_ctx, Hkv, chunk_keys=0, s=None):
+    return L.load().b200_attn_reserve(kv_type, max_slots, q_len, max_n, n_ctx, Hkv, chunk_keys, _stream(s)) == L.OK
 
 
 def attn_decode_slots_partial(q, c, part_o, part_m, part_l, n_slots, q_len, pos, max_n, Hq, scale, chunk_keys=0, s=None):

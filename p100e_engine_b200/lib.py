@@ -60,7 +60,7 @@ SIGNATURES = {
     "b200_attn_dec2_set_nsplit": (None, [I]),
     "b200_attn_dec2_reload_env": (I, []),
     "b200_attn_fixed_chunk": (I, [I]),
-    "b200_attn_reserve": (I, [I, I, I, I, I, I, P]),
+    "b200_attn_reserve": (I, [U32, I, I, I, I, I, I, P]),
     "b200_attn_decode_slots": (I, [P, KVP, P, P, I, I, P, I, I, F, I, P]),
     "b200_attn_decode_slots_a16": (I, [P, KVP, P, P, P, I, I, P, I, I, F, I, P]),
     "b200_noalloc_device_status": (I, [P]),

@@ -339,7 +339,7 @@ def test_reserve_then_calls_allocate_nothing(cuda, lib):
     torch.cuda.synchronize()
     s = torch.cuda.Stream()
     with torch.cuda.stream(s):
-        assert fast.attn_reserve(8, 4, 8192, maxp << 8, HKV, 64)
+        assert fast.attn_reserve(kt, 8, 4, 8192, maxp << 8, HKV, 64)
         torch.cuda.synchronize()
         free0 = torch.cuda.mem_get_info()[0]
         for chunk in (64, 256, 1024):
