@@ -69,9 +69,9 @@ def parse():
     ap.add_argument("--chunk", type=int, default=-1, help="keys per split (-1 = chosen from the batch)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-prefill", action="store_true", help="leave the prefill record out of the decode line")
-    ap.add_argument("--no-graph", action="store_true", help="never replay the step from a CUDA graph")
     ap.add_argument("--breakdown", action="store_true", help="add per-layer times of the step's parts (an extra eager pass)")
     ap.add_argument("--q-len", type=int, default=0, help="override the workload's query rows per slot (1..4)")
+    ap.add_argument("--seq-shards", type=int, default=0, help="force the number of sequence shards (default: only when N > 4)")
     ap.add_argument("--seed", type=int, default=0xB200)
     return ap.parse_args()
 
@@ -363,12 +363,15 @@ class Workload:
             from p100e_engine_b200 import dist as Dm
             import torch.distributed as dist
             groups = [dist.new_group(r) for r in plan.all_merge_groups()]
-            in_groups = [dist.new_group(r) for r in plan.all_merge_groups()]
-            self.in_group = in_groups[plan.head_rank]
+            group, ranks = groups[plan.head_rank], plan.merge_group_ranks()
             self.nsub = 2 if slots >= 2 else 1
             cut = [slots * i // self.nsub for i in range(self.nsub + 1)]
             self.sub = [(cut[i], cut[i + 1]) for i in range(self.nsub)]
-            self.merge = [Dm.SeqMerge(plan, (b - a) * q_len, hq, D, dev, groups[plan.head_rank]) for a, b in self.sub]
+            # one raw NCCL communicator per stream that exchanges (the two sub-batch streams, the upload stream): the
+            # collectives are enqueued on those streams themselves
+            self.comms = [Dm.NcclComm(ranks, group, dev) for _ in range(self.nsub + 1)]
+            self.in_comm = self.comms[self.nsub]
+            self.merge = [Dm.SeqMerge(plan, (b - a) * q_len, hq, D, dev, group, self.comms[i]) for i, (a, b) in enumerate(self.sub)]
             self.sub_streams = [torch.cuda.Stream() for _ in range(self.nsub)]
             self.ev_prep = torch.cuda.Event()
             self.ev_sub = [torch.cuda.Event() for _ in range(self.nsub)]
@@ -491,7 +494,7 @@ class Workload:
                     self.h2d_stream.wait_event(self.ev_used[b])
                 self.stage[b][r].copy_(self.h_in[l], non_blocking=True)
                 if self.plan.n_seq > 1:
-                    dist.all_gather_into_tensor(self.stage[b].view(-1), self.stage[b][r], group=self.in_group)
+                    self.in_comm.all_gather_f32(self.stage[b], self.h2d_stream)
                 self.ev_in[b].record(self.h2d_stream)
             main.wait_event(self.ev_in[b])
             if l >= 2:
@@ -517,9 +520,9 @@ class Workload:
         if self.merge is not None:
             import torch.distributed as dist
             from p100e_engine_b200 import dist as Dm
-            names += ["all-gather of (O, m, l) in the pair (NCCL)", "merge of the shards + gate"]
+            names += ["copy into place + all-gather of (O, m, l) in the pair (NCCL)", "merge of the shards + gate"]
             if not hasattr(self, "bd_merge"):
-                self.bd_merge = Dm.SeqMerge(self.plan, self.rows, self.hq, D, self.dev, self.merge[0].group)
+                self.bd_merge = Dm.SeqMerge(self.plan, self.rows, self.hq, D, self.dev, self.merge[0].group, self.comms[0])
             mg = self.bd_merge
         acc = np.zeros(len(names))
         host = 0.0
@@ -542,7 +545,8 @@ class Workload:
                     ok = ok and fast.attn_decode_slots_partial(self.q, c, po, pm, pl, self.slots, self.q_len, self.last_key, self.max_n,
                                                                self.hq, SCALE, self.chunk)
                     ev[l][2].record()
-                    dist.all_gather_into_tensor(mg.recv.view(-1), mg.send, group=mg.group)
+                    mg.recv[self.plan.seq_rank].copy_(mg.send)
+                    mg.comm.all_gather_f32(mg.recv)
                     ev[l][3].record()
                     ok = ok and fast.seq_exchange_merge(0, self.plan.n_seq, mg.send, mg.recv, mg.R, D, self.gate, self.out.view(mg.R, D))
                     ev[l][4].record()
@@ -606,7 +610,7 @@ def run_b200(args):
 
     world, rank, local, dev = dist_setup()
     lib = L.load()
-    plan = Dm.ShardPlan(world, rank, HKV, 6)
+    plan = Dm.ShardPlan(world, rank, HKV, 6, args.seq_shards or None)
     wl = Workload(args, plan, dev, local)
 
     def barrier():
@@ -627,64 +631,24 @@ def run_b200(args):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
-    def captured(fn):
-        """the step as a CUDA graph (launch gaps matter once a layer takes a fraction of a millisecond); None if capture fails"""
-        try:
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                fn()
-            g.replay()
-            torch.cuda.synchronize()
-            return g
-        except Exception as e:   # noqa: BLE001 - any capture problem falls back to eager launches
-            sys.stderr.write("bench.py: graph capture failed, launching eagerly (%s)\n" % str(e).splitlines()[0])
-            torch.cuda.synchronize()
-            return None
-
     for _ in range(max(args.warmup, 3)):
         wl.step()
     barrier()
-    # Steps that take a few milliseconds are replayed from a CUDA graph (sequence-sharded runs: ~100 launches and 32
-    # collectives per step); the per-call events that feed the roofline then come from an eager pass of the same steps.
-    use_graph = plan.n_seq > 1 and not args.no_graph
-    graph = captured(lambda: wl.step()) if use_graph else None
-    if world > 1:   # every rank must take the same path
-        flag = torch.tensor([1 if graph is not None else 0], device=dev)
-        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-        if int(flag.item()) == 0:
-            graph = None
     events = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(wl.layers)]
               for _ in range(args.steps)]
     clk = ClockSampler(local)
     clk.start()
     n0 = lib.b200_launch_count()
-    if graph is not None:
-        ms_total = timed(lambda ev: graph.replay(), args.steps)
-        launches = (lib.b200_launch_count() - n0)
-        for _ in range(2):
-            wl.step()
-        n1 = lib.b200_launch_count()
-        ms_eager = timed(lambda ev: wl.step(ev), args.steps, events)
-        launches = lib.b200_launch_count() - n1     # a replay launches what the eager step launches
-    else:
-        ms_total = timed(lambda ev: wl.step(ev), args.steps, events)
-        launches = lib.b200_launch_count() - n0
-        ms_eager = ms_total
-    clocks = clocks_under_load(local, clk.stop(), (lambda: graph.replay()) if graph is not None else (lambda: wl.step(None)),
-                               ms_total, args.steps)
+    ms_total = timed(lambda ev: wl.step(ev), args.steps, events)
+    launches = lib.b200_launch_count() - n0
+    clocks = clocks_under_load(local, clk.stop(), lambda: wl.step(None), ms_total, args.steps)
     att_ms = [e0.elapsed_time(e1) for st in events for (e0, e1) in st]
     att_ms_avg = float(np.mean(att_ms))
     # ---- end to end: host buffers in, host results out ----
     for _ in range(3):
         wl.step_e2e()
     barrier()
-    graph_e2e = captured(lambda: wl.step_e2e()) if use_graph and graph is not None else None
-    if world > 1:
-        flag = torch.tensor([1 if graph_e2e is not None else 0], device=dev)
-        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-        if int(flag.item()) == 0:
-            graph_e2e = None
-    ms_e2e = timed((lambda ev: graph_e2e.replay()) if graph_e2e is not None else (lambda ev: wl.step_e2e()), args.steps)
+    ms_e2e = timed(lambda ev: wl.step_e2e(), args.steps)
     status = lib.b200_last_device_status(None)
     if status:
         raise SystemExit("bench.py: a kernel recorded device status %d" % status)
@@ -712,23 +676,19 @@ def run_b200(args):
     line = base_line(args, wl.slots, wl.q_len, wl.layers)
     line["config"].update({"parallelism": "kv-head shards %d x sequence shards %d" % (plan.n_head_shards, plan.n_seq),
                            "keys_per_layer": int(wl.n_ctx.sum()), "chunk_keys": args.chunk,
-                           "launch": "CUDA graph replay of the step" if graph is not None else "eager launches",
                            "l2": "inputs larger than L2 (%.1f GB of KV per step per GPU)" % (wl.kv_bytes_layer * wl.layers / 1e9),
                            "step": "per layer: attn_prep (norm+RoPE+quantise+append) + split-KV attention + sigmoid gate"})
     line.update({"value": value, "ms_per_step": ms_step, "dtype": "f16 operands, fp32 accumulate",
                  "clocks": clocks, "gpu_launches": int(launches), "out_fingerprint": fingerprint,
                  "e2e": {"value": total_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
-                         "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-                         "launch": "CUDA graph replay" if graph_e2e is not None else "eager launches"},
+                         "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
                  "roofline": {"bound": "hbm", "kernel": "decode_part_k (+ work list, chunk merge) per layer call", "achieved": achieved,
                               "peak": peak, "peak_source": "measured" if peaks else "fallback", "unit": "GB/s",
                               "frac": achieved / peak,
                               "traffic": int(tr["dram_bytes_per_kv_byte"] * wl.kv_bytes_layer) if tr else None,
                               "traffic_source": tr.get("source"),
                               "avg_launch_ms": att_ms_avg, "algorithmic_bytes_per_launch": int(wl.kv_bytes_layer),
-                              "timing": "CUDA events around each layer's attention call on the launching stream, " +
-                                        ("in an eager pass of the same steps (%.3f ms per step; the timed value replays a graph)" % (ms_eager / args.steps)
-                                         if graph is not None else "inside the timed region")}})
+                              "timing": "CUDA events around each layer's attention call on the launching stream, inside the timed region"}})
     if bd is not None:
         line["breakdown"] = bd
     if prefill is not None:
@@ -805,7 +765,7 @@ def prefill_measure(args, world, rank, local, dev, steps, warmup, cpu=True):
     import torch.distributed as dist
     from p100e_engine_b200 import dist as Dm, fast, lib as L, pool as P
     lib = L.load()
-    plan = Dm.ShardPlan(world, rank, HKV, 6)
+    plan = Dm.ShardPlan(world, rank, HKV, 6, args.seq_shards or None)
     hkv, hq, n_seq = plan.hkv_local, plan.hq_local, plan.n_seq
     T = WORKLOADS["prefill8k"][2]
     kt = KV_TYPES["q8_0"]
@@ -833,6 +793,7 @@ def prefill_measure(args, world, rank, local, dev, steps, warmup, cpu=True):
     if n_seq > 1:
         groups = [dist.new_group(r) for r in plan.all_merge_groups()]
         group = groups[plan.head_rank]
+        comm = Dm.NcclComm(plan.merge_group_ranks(), group, dev)
         qr = torch.empty(T, hq, D, device=dev)
         R = T * hq
         send = torch.empty(R * (D + 2), device=dev)
@@ -860,9 +821,8 @@ def prefill_measure(args, world, rank, local, dev, steps, warmup, cpu=True):
                                                   scratch, nb)
             if ev is not None:
                 ev[1].record()
-            dist.all_gather_into_tensor(recv.view(-1), send, group=group)
             gate32.copy_(gt)
-            ok = ok and fast.seq_exchange_merge(0, n_seq, send, recv, R, D, gate32.view(R, D), out32.view(R, D))
+            ok = ok and fast.seq_exchange_merge(comm.handle, n_seq, send, recv, R, D, gate32.view(R, D), out32.view(R, D))
             out.copy_(out32)
         if not ok:
             raise RuntimeError("a library call was refused")

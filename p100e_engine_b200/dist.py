@@ -41,12 +41,13 @@ class ShardPlan:
     n_kv_heads, the remaining factor splits the sequence; ranks sharing a head group form one merge group.
     """
 
-    def __init__(self, world, rank, n_kv_heads=4, gqa=6):
+    def __init__(self, world, rank, n_kv_heads=4, gqa=6, n_seq=None):
         if world < 1 or rank < 0 or rank >= world:
             raise ValueError("bad world / rank")
         self.world, self.rank = world, rank
-        self.n_head_shards = min(world, n_kv_heads)
-        if n_kv_heads % self.n_head_shards or world % self.n_head_shards:
+        # n_seq forces the number of sequence shards (the default uses them only when the ranks outnumber the kv heads)
+        self.n_head_shards = min(world, n_kv_heads) if not n_seq else world // n_seq
+        if self.n_head_shards < 1 or n_kv_heads % self.n_head_shards or world % self.n_head_shards:
             raise ValueError("world size %d does not tile %d kv heads" % (world, n_kv_heads))
         self.n_seq = world // self.n_head_shards
         self.head_rank = rank // self.n_seq
@@ -70,12 +71,66 @@ class ShardPlan:
         return seq_local_length(n, self.n_seq, self.seq_rank, psh)
 
 
+class NcclComm:
+    """A raw ncclComm_t over `ranks` (global ranks, in shard order), made with the NCCL library that torch has loaded: the
+    library's exchange entry point and plain all-gathers are then enqueued straight on the caller's stream, without the
+    process group's own stream and the two event hops around every collective.  Collective: every rank of `ranks` constructs
+    it at the same point; the unique id travels over the torch process group `group` (the same ranks)."""
+
+    def __init__(self, ranks, group, device):
+        import ctypes as C
+        import torch
+        import torch.distributed as dist
+        paths = [ln.split()[-1] for ln in open("/proc/self/maps") if "libnccl" in ln]
+        if not paths:
+            raise RuntimeError("no NCCL library is loaded in this process")
+        self.nccl = C.CDLL(paths[0])
+
+        class UniqueId(C.Structure):
+            _fields_ = [("internal", C.c_byte * 128)]
+
+        uid = UniqueId()
+        me = dist.get_rank()
+        if me == ranks[0] and self.nccl.ncclGetUniqueId(C.byref(uid)) != 0:
+            raise RuntimeError("ncclGetUniqueId failed")
+        t = torch.frombuffer(bytearray(bytes(uid)), dtype=torch.uint8).to(device)
+        dist.broadcast(t, ranks[0], group=group)
+        C.memmove(C.byref(uid), t.cpu().numpy().tobytes(), 128)
+        self.comm = C.c_void_p()
+        self.nccl.ncclCommInitRank.argtypes = [C.POINTER(C.c_void_p), C.c_int, UniqueId, C.c_int]
+        if self.nccl.ncclCommInitRank(C.byref(self.comm), len(ranks), uid, ranks.index(me)) != 0:
+            raise RuntimeError("ncclCommInitRank failed")
+        self.nccl.ncclAllGather.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p, C.c_void_p]
+        self.nccl.ncclCommDestroy.argtypes = [C.c_void_p]
+        self.rank, self.size = ranks.index(me), len(ranks)
+
+    @property
+    def handle(self):
+        return self.comm.value
+
+    def all_gather_f32(self, buf, stream=None):
+        """in-place all-gather of a float32 tensor [size][n]: this rank's row is its contribution (on the current stream)"""
+        import torch
+        n = buf.numel() // self.size
+        st = (stream or torch.cuda.current_stream()).cuda_stream
+        rc = self.nccl.ncclAllGather(buf.data_ptr() + 4 * n * self.rank, buf.data_ptr(), n, 7, self.comm, st)
+        if rc != 0:
+            raise RuntimeError("ncclAllGather returned %d" % rc)
+
+    def close(self):
+        if self.comm:
+            self.nccl.ncclCommDestroy(self.comm)
+            self.comm = None
+
+
 class SeqMerge:
     """All-gather + merge of sequence-shard partials inside one merge group (used only when plan.n_seq > 1)."""
 
-    def __init__(self, plan, rows, hq_local, d=256, device=None, group=None):
+    def __init__(self, plan, rows, hq_local, d=256, device=None, group=None, comm=None):
+        """group: torch process group of the shards (the exchange then runs through torch.distributed); comm: a NcclComm of
+        the shards (the exchange and the merge are then one library call on the current stream)"""
         import torch
-        self.plan, self.rows, self.hq, self.d, self.group = plan, rows, hq_local, d, group
+        self.plan, self.rows, self.hq, self.d, self.group, self.comm = plan, rows, hq_local, d, group, comm
         R = rows * hq_local
         self.R = R
         # one flat send buffer per rank: [O (R*d) | m (R) | l (R)], gathered into [n_seq][R*(d+2)]
@@ -91,6 +146,10 @@ class SeqMerge:
         import torch.distributed as dist
         from . import fast
         R, d = self.R, self.d
+        if self.comm is not None:
+            if not fast.seq_exchange_merge(self.comm.handle, self.plan.n_seq, self.send, self.recv, R, d, gate, out):
+                raise RuntimeError("seq_exchange_merge refused")
+            return
         dist.all_gather_into_tensor(self.recv.view(-1), self.send, group=self.group)
         # the merge reads the gathered flat buffers in place (no communicator: the gather above was the exchange)
         if not fast.seq_exchange_merge(0, self.plan.n_seq, self.send, self.recv, R, d, gate, out):
