@@ -58,6 +58,8 @@ SIGNATURES = {
     "b200_attn_decode2": (I, [P, KVP, P, I, I, P, I, F, P, P]),
     "b200_attn_dec2_nsplit": (I, [I]),
     "b200_attn_dec2_set_nsplit": (None, [I]),
+    "b200_attn_dec_tc": (I, []),
+    "b200_attn_dec_set_tc": (None, [I]),
     "b200_attn_dec2_reload_env": (I, []),
     "b200_attn_fixed_chunk": (I, [I]),
     "b200_attn_reserve": (I, [U32, I, I, I, I, I, I, P]),

@@ -267,6 +267,26 @@ def test_verify_batch_vs_oracle(cuda, lib, tname, chunk):
     util.check_close(got, ref, "verify batch %s chunk=%d" % (tname, chunk))
 
 
+@pytest.mark.parametrize("tname", ["q8_0", "q4_0"])
+@pytest.mark.parametrize("q_len", [1, 2, 3, 4])
+def test_even_split_kernels_agree(cuda, lib, tname, q_len):
+    """the even split runs quantised caches on the tcgen05 kernel; the mma.sync kernel (set_tc(0)) must give the same
+    result within the tolerance, and both must match the oracle, for every row count and ragged contexts"""
+    lens = [5000, 130, 64, 4, 2049, 767, 128, 1]
+    lens = [max(n, q_len) for n in lens]
+    assert lib.b200_attn_dec_tc() == 1
+    got_tc, ref, _ = _verify_batch(cuda, TYPES[tname], len(lens), q_len, lens, 11 + q_len, -1)
+    try:
+        lib.b200_attn_dec_set_tc(0)
+        assert lib.b200_attn_dec_tc() == 0
+        got_mma, _, _ = _verify_batch(cuda, TYPES[tname], len(lens), q_len, lens, 11 + q_len, -1)
+    finally:
+        lib.b200_attn_dec_set_tc(1)
+    util.check_close(got_tc, ref, "even split, tcgen05 kernel (%s, q_len %d)" % (tname, q_len))
+    util.check_close(got_mma, ref, "even split, mma.sync kernel (%s, q_len %d)" % (tname, q_len))
+    util.check_close(got_tc, got_mma, "tcgen05 vs mma.sync (%s, q_len %d)" % (tname, q_len))
+
+
 def test_slot_rows_independent_of_batch(cuda, lib):
     """a slot's rows are bitwise the same whether it is decoded alone or inside a batch (same chunk)"""
     import torch
