@@ -1441,6 +1441,13 @@ int b200_attn_dec2_nsplit(int Hkv) {
     return g_nsplit_override > 0 ? g_nsplit_override : MAX_DEFAULT_CHUNKS;
 }
 void b200_attn_dec2_set_nsplit(int n) { g_nsplit_override = n > 0 ? n : 0; }
+#ifdef TC_PROF
+int b200_debug_tc_prof(unsigned long long * out, int reset) {
+    if (out && cudaMemcpyFromSymbol(out, g_tc_prof, sizeof(unsigned long long) * 16) != cudaSuccess) return B200_ERR_CUDA;
+    if (reset) { unsigned long long z[16] = {0}; cudaMemcpyToSymbol(g_tc_prof, z, sizeof z); }
+    return B200_OK;
+}
+#endif
 int b200_attn_dec_tc(void) { return tc_enabled() ? 1 : 0; }
 void b200_attn_dec_set_tc(int on) { g_tc = on < 0 ? -1 : on ? 1 : 0; }
 int b200_attn_dec2_reload_env(void) {

@@ -4,32 +4,48 @@
 //
 // One CTA per SM walks its run of keys in tiles of 128.  Per tile and kv head:
 //   K rows (TMA -> staging) --16 worker warps: int8 / nibble -> f16 * block scale--> tensor memory, lane = key
-//   S^T[128 keys x rows]  = K (A operand in tensor memory) * Q^T (B operand, K-major image in shared memory)
+//   S^T[128 keys x rows]   = K (A operand in tensor memory) * Q^T (B operand, K-major image in shared memory)
 //   V rows (TMA -> staging) --workers--> f16 image [key][dim] in shared memory
 //   workers: S^T -> mask -> P = 2^(S - reference maximum + 8) as f16 -> P image [row][key] in shared memory
-//   O[rows x 256] += P (A operand, shared memory) * V (B operand, MN-major image)
+//   O^T[256 dims x rows]  += V^T (A operand, the MN-major image, two halves of 128 dims) * P^T (B operand, K-major image)
 // The MMAs and the TMA copies are issued by one thread of a 17th warp; the workers meet it through mbarriers only, and each
-// other once per tile (the vote on "some score outgrew its reference maximum").  Against the mma.sync kernel this takes
-// the multiply-adds, the fragment shuffling and the per-tile accumulator traffic out of the instruction stream: what the
-// CUDA cores still do is the widening of 2 x 128 x 256 cache values per tile and 128 x rows exponentials.
+// other once per tile (the vote on "some score outgrew its reference maximum").  K and S^T are double-buffered in tensor
+// memory: the workers widen the K rows of tile i + 1 before they turn to V and the scores of tile i, so the Q K^T of a tile
+// has a whole conversion phase to finish.  Against the mma.sync kernel this takes the multiply-adds, the fragment
+// shuffling and the per-tile accumulator traffic out of the instruction stream: what the CUDA cores still do is the
+// widening of 2 x 128 x 256 cache values per tile and 128 x rows exponentials.
 //
 // Every wait is bounded (mbar_wait gives up after two seconds and records ST_WAIT_TIMEOUT).
 
 constexpr int UT = 128;                       // keys per tile
-constexpr int TC_WORKERS = 512, TC_THR = TC_WORKERS + 32;
-constexpr int TC_NBUF = 3;                    // staging ring: K(i), V(i), K(i+1), V(i+1), .. walk three buffers
+constexpr int TC_WORKERS = 512, TC_THR = TC_WORKERS + 64;   // 16 worker warps, the MMA warp, the TMA warp
+constexpr int TC_NBUF = 4;                    // staging ring, in the order the workers consume: K0, K1, V0, K2, V1, ..
 constexpr int TC_HDR = 2048;                  // barriers, reference maxima, exchange arrays, page entries
-constexpr int TC_PGS = 256;                   // page-table entries of a run kept in shared memory
+constexpr int TC_PGS = 224;                   // page-table entries of a run kept in shared memory
 constexpr int TC_VF = UT * DH * 2;            // f16 image of a tile's V rows
 constexpr int TC_QI = 32 * 32 * 16;           // f16 image of up to 32 query rows
 constexpr int TC_PLBO = 528;                  // bytes between the 8-key chunks of the P image (512 + 16: stores of a warp spread over the banks)
-constexpr int TC_PI = 10240;                  // P image: 16 chunks, read as 128 rows (rows >= 32 alias the following chunks)
+constexpr int TC_PI = 8704;                   // P image: 16 chunks of up to 32 rows
 
 template <uint32_t KT> constexpr size_t tc_smem_bytes() { return TC_HDR + (size_t) TC_NBUF * UT * traits<KT>::HB + TC_VF + TC_QI + TC_PI; }
 
 __device__ __forceinline__ void tc_arrive(uint64_t * bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// a wait that records which one gave up (bits 8.. of the status word, beside ST_WAIT_TIMEOUT)
+__device__ __forceinline__ void tc_wait(uint64_t * bar, uint32_t parity, unsigned * status, int site) {
+    if (!mbar_wait(bar, parity, status)) atomicOr(status, 0x100u << site);
+}
+#ifdef TC_PROF
+__device__ unsigned long long g_tc_prof[16];
+#define TC_T(v) const long long v = clock64()
+#define TC_MARK(v) v = clock64()
+#define TC_ACC(slot, t0, t1) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (threadIdx.x == 0 || threadIdx.x >= TC_WORKERS)) atomicAdd(&g_tc_prof[slot], (unsigned long long) ((t1) - (t0))); } while (0)
+#else
+#define TC_T(v)
+#define TC_MARK(v)
+#define TC_ACC(slot, t0, t1)
+#endif
 __device__ __forceinline__ void tc_bar_workers() { asm volatile("bar.sync 1, %0;" ::"n"(TC_WORKERS) : "memory"); }
 __device__ __forceinline__ int tc_vote_workers(int v) {
     int r;
@@ -39,13 +55,14 @@ __device__ __forceinline__ int tc_vote_workers(int v) {
 }
 
 // One 32-value block of a cache row -> 16 registers of f16 pairs (register m = dims 2m, 2m+1 of the block), each value the
-// rounded product of the stored integer and the block's f16 scale.
+// rounded product of the stored integer and the block's f16 scale.  live = false gives zeros whatever the bytes are (the
+// integer part is finite for every bit pattern; only the scale is replaced).
 template <uint32_t KT>
-__device__ __forceinline__ void tc_block(const unsigned char * row, int blk, uint32_t (&r)[16]) {
+__device__ __forceinline__ void tc_block(const unsigned char * row, int blk, bool live, uint32_t (&r)[16]) {
     if constexpr (KT == B200_KV_Q8_0) {
         const uint4 a = *reinterpret_cast<const uint4 *>(row + 16 + 32 * blk), b = *reinterpret_cast<const uint4 *>(row + 32 + 32 * blk);
-        const uint32_t sc = *reinterpret_cast<const uint16_t *>(row + 2 * blk);
-        const uint32_t d2 = sc | (sc << 16);
+        const uint32_t sc = live ? *reinterpret_cast<const uint16_t *>(row + 2 * blk) : 0u;
+        const uint32_t d2 = __byte_perm(sc, sc, 0x1010);
         const uint32_t wv[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -59,7 +76,7 @@ __device__ __forceinline__ void tc_block(const unsigned char * row, int blk, uin
         if ((blk & 1) == 0) {
             const uint32_t * p = reinterpret_cast<const uint32_t *>(row + 18 * blk);
             const uint32_t w0 = p[0], w1 = p[1], w2 = p[2], w3 = p[3], w4 = p[4];
-            sc = w0 & 0xffffu;
+            sc = w0;
             q[0] = __funnelshift_r(w0, w1, 16); q[1] = __funnelshift_r(w1, w2, 16);
             q[2] = __funnelshift_r(w2, w3, 16); q[3] = __funnelshift_r(w3, w4, 16);
         } else {
@@ -67,7 +84,8 @@ __device__ __forceinline__ void tc_block(const unsigned char * row, int blk, uin
             sc = p[0] >> 16;
             q[0] = p[1]; q[1] = p[2]; q[2] = p[3]; q[3] = p[4];
         }
-        const uint32_t d2 = sc | (sc << 16);
+        if (!live) sc = 0u;
+        const uint32_t d2 = __byte_perm(sc, sc, 0x1010);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const uint32_t lo = q[j] & 0x0f0f0f0fu, hi = (q[j] >> 4) & 0x0f0f0f0fu;
@@ -86,7 +104,8 @@ __global__ void __launch_bounds__(TC_THR, 1)
 decode_tc_k(const dec_args a, const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV) {
     extern __shared__ __align__(1024) unsigned char smem[];
     constexpr int HB = traits<KT>::HB, BUF = UT * HB;
-    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int w = __shfl_sync(0xffffffffu, tid >> 5, 0);   // the warp index as a warp-uniform value
     const bool worker = w < TC_WORKERS / 32;
     const int lq = w & 3, gq = (w >> 2) & 3;     // worker warp: tensor-memory lane quarter, column / block group
     const int hk = (int) (blockIdx.x % (unsigned) a.g.Hkv), ui = (int) (blockIdx.x / (unsigned) a.g.Hkv);
@@ -95,18 +114,24 @@ decode_tc_k(const dec_args a, const __grid_constant__ CUtensorMap mapK, const __
     if (s0 >= s1) return;
 
     uint64_t * full = reinterpret_cast<uint64_t *>(smem);                       // [TC_NBUF] staging buffer filled
-    uint64_t * s_full = full + 4, * pv_done = full + 5, * kconv = full + 6, * p_ready = full + 7;
-    uint32_t * tbase_p = reinterpret_cast<uint32_t *>(smem + 64);
+    uint64_t * s_full = full + 4;                                                // [2] Q K^T of a tile has landed in S^T buffer b
+    uint64_t * kconv = full + 6;                                                 // [2] K of a tile is in tensor-memory buffer b (per buffer: the
+                                                                                 // workers run up to a tile ahead of the issuer)
+    uint64_t * p_ready = full + 8;                                               // [2] P and the V image of a tile are written
+    uint64_t * pv_done = full + 10;
+    uint32_t * tbase_p = reinterpret_cast<uint32_t *>(smem + 96);
     float * mref = reinterpret_cast<float *>(smem + 128);                        // [32] reference maximum per column (log2 units)
     float * fsc = reinterpret_cast<float *>(smem + 256);                         // [32] rescale factor of the last move
     float * wx = reinterpret_cast<float *>(smem + 384);                          // [4][32] per lane quarter: maxima / sums
-    int * pgs = reinterpret_cast<int *>(smem + 1024);                            // [TC_PGS]
+    float2 * mm = reinterpret_cast<float2 *>(smem + 896);                        // [32] (reference + REF_GAP, finite reference - PSHIFT)
+    int * pgs = reinterpret_cast<int *>(smem + 1152);                            // [TC_PGS]
     unsigned char * stg = smem + TC_HDR, * VF = stg + TC_NBUF * BUF, * QI = VF + TC_VF, * PI = QI + TC_QI;
 
     if (tid == 0) {
         for (int b = 0; b < TC_NBUF; ++b) mbar_init(&full[b], 1);
-        mbar_init(s_full, 1); mbar_init(pv_done, 1);
-        mbar_init(kconv, TC_WORKERS / 32); mbar_init(p_ready, TC_WORKERS / 32);
+        mbar_init(&s_full[0], 1); mbar_init(&s_full[1], 1); mbar_init(pv_done, 1);
+        mbar_init(&kconv[0], TC_WORKERS / 32); mbar_init(&kconv[1], TC_WORKERS / 32);
+        mbar_init(&p_ready[0], TC_WORKERS / 32); mbar_init(&p_ready[1], TC_WORKERS / 32);
         mbar_fence_init();
     }
     if (w == TC_WORKERS / 32) umma::tmem_alloc(tbase_p, 512);
@@ -116,11 +141,15 @@ decode_tc_k(const dec_args a, const __grid_constant__ CUtensorMap mapK, const __
     __syncthreads();
     umma::fence_after_sync();
     const uint32_t tb = *tbase_p;
-    const uint32_t tA = tb, tS = tb + 128, tO = tb + 256;   // K as f16 pairs (128 columns), S^T (NC), O (256)
+    // tensor memory: K as f16 pairs (2 x 128 columns), S^T (2 x 32), O^T (two halves of 128 dims, NC columns each)
+    const uint32_t tA = tb, tS = tb + 256, tO = tb + 320;
     const uint32_t lane_off = (uint32_t) (32 * lq) << 16;
     const int R = a.q_len * GQA;
+    // the O^T columns this worker warp rescales and writes out: half hO of the dims, columns 16 cO .. 16 cO + 15
+    const int hO = gq & 1, cO = gq >> 1;
+    const bool o_warp = 16 * cO < NC;
 
-    int g = 0;   // tiles this CTA has walked: parities of the per-tile barriers; 2 g = staging items before the run
+    int g = 0;   // tiles this CTA has walked (parities of the per-tile barriers); 2 g = staging items before the run
     for (int sg = s0; sg < s1; ++sg) {
         const int4 seg = a.segs[sg];
         const int slot = seg.x, k_lo = seg.y;
@@ -136,6 +165,10 @@ decode_tc_k(const dec_args a, const __grid_constant__ CUtensorMap mapK, const __
         if (nt == 0) continue;
         const int32_t * tab = a.g.pt ? a.g.pt + (a.g.rtab ? a.g.rtab[slot * a.q_len] : 0) : nullptr;
         const int pg0 = tab ? k_lo >> a.g.psh : 0;
+        const int ib = 2 * g;
+        // staging item of a tile's K rows / V rows in consumption order: K0, K1, V0, K2, V1, .., K(nt-1), V(nt-2), V(nt-1)
+        auto item_k = [&](int j) { return j == 0 ? 0 : 2 * j - 1; };
+        auto item_v = [&](int j) { return j < nt - 1 ? 2 * j + 2 : 2 * nt - 1; };
 
         if (worker) {
             if (tab) {
@@ -154,55 +187,99 @@ decode_tc_k(const dec_args a, const __grid_constant__ CUtensorMap mapK, const __
                 }
                 *reinterpret_cast<uint4 *>(QI + grp * 128 + kc * (NC * 16) + hh * 16) = pk;
             }
-            if (tid < 32) mref[tid] = B200_NEG_INF;
+            if (tid < 32) { mref[tid] = B200_NEG_INF; mm[tid] = make_float2(B200_NEG_INF, -PSHIFT); }
             umma::fence_async_smem();
         }
         __syncthreads();
 
         if (!worker) {
-            // ---------------- issuer: TMA copies and MMAs ----------------
-            if (lane == 0) {
-                auto issue = [&](int q) {   // item q of the run: K rows of tile q / 2 (q even) or its V rows (q odd)
-                    if (q >= 2 * nt) return;
-                    const int p_t = k_lo + (q >> 1) * UT;
-                    const int buf = (2 * g + q) % TC_NBUF;
+            // ---------------- two issuer warps: MMAs (warp 16) and TMA copies (warp 17) ----------------
+            // All 32 lanes walk the loops and wait, so that counters, addresses and descriptors are warp-uniform values
+            // (the MMA and TMA instructions take their operands from uniform registers); one elected lane issues.  The
+            // copies have a warp of their own because a TMA instruction can hold its thread for as long as the copy
+            // unit's queue is full, which must not delay the next MMA.
+            const bool lead = umma::elect_one();
+            const int nt_u = __shfl_sync(0xffffffffu, nt, 0), g_u = __shfl_sync(0xffffffffu, g, 0);
+            if (w == TC_WORKERS / 32) {
+                const uint32_t tb_u = __shfl_sync(0xffffffffu, tb, 0);
+                const uint32_t tA_u = tb_u, tS_u = tb_u + 256, tO_u = tb_u + 320;
+                constexpr uint32_t id_qk = umma::idesc_f16(UT, NC, false, false);   // S^T[128 x NC] = K (tensor memory) * Q^T (K-major)
+                constexpr uint32_t id_pv = umma::idesc_f16(UT, NC, true, false);    // O^T[128 x NC] += V^T (MN-major) * P^T (K-major)
+                const uint32_t q_s = smem_u32(QI), p_s = smem_u32(PI), v_s = smem_u32(VF);
+                auto qk = [&](int j) {   // tile j: waits for its K in tensor memory, queues Q K^T
+                    const int G = g_u + j, b = G & 1;
+                    TC_T(q0);
+                    tc_wait(&kconv[b], (uint32_t) ((G >> 1) & 1), a.status, 0);
+                    TC_T(q1);
+                    TC_ACC(8, q0, q1);
+                    umma::fence_after_sync();
+                    if (lead) {
+#pragma unroll
+                        for (int ks = 0; ks < DH / 16; ++ks)
+                            umma::mma_ts(tS_u + 32 * b, tA_u + 128 * b + ks * 8, umma::smem_desc(q_s + ks * 2 * (NC * 16), NC * 16, 128), id_qk, ks > 0);
+                        umma::commit(&s_full[b]);
+                    }
+                    TC_T(q2);
+                    TC_ACC(12, q1, q2);
+                };
+                qk(0);
+                for (int i = 0; i < nt_u; ++i) {
+                    if (i + 1 < nt_u) qk(i + 1);
+                    const int G = g_u + i;
+                    TC_T(p0);
+                    tc_wait(&p_ready[G & 1], (uint32_t) ((G >> 1) & 1), a.status, 1);     // P and the V image are in place
+                    TC_T(p1);
+                    TC_ACC(10, p0, p1);
+                    umma::fence_after_sync();
+                    if (lead) {
+#pragma unroll
+                        for (int ks = 0; ks < UT / 16; ++ks)
+#pragma unroll
+                            for (int h = 0; h < 2; ++h)   // V image: 8-key groups 4096 apart (LBO), 8-dim groups 128 apart (SBO); P: 8-key chunks TC_PLBO apart
+                                umma::mma_ss(tO_u + h * NC, umma::smem_desc(v_s + ks * 2 * 4096 + h * 2048, 4096, 128),
+                                             umma::smem_desc(p_s + ks * 2 * TC_PLBO, TC_PLBO, 128), id_pv, (i > 0 || ks > 0) ? 1u : 0u);
+                        umma::commit(pv_done);
+                    }
+                    TC_T(p2);
+                    TC_ACC(13, p1, p2);
+                }
+            } else {
+                const int klo_u = __shfl_sync(0xffffffffu, k_lo, 0), khi_u = __shfl_sync(0xffffffffu, k_hi, 0);
+                const int pg0_u = __shfl_sync(0xffffffffu, pg0, 0), ib_u = 2 * g_u;
+                for (int q = 0; q < 2 * nt_u; ++q) {   // staging item q of the run, in the order the workers consume them
+                    if (q >= TC_NBUF) {
+                        // its buffer held item q - 4: the K rows of a tile are free once every worker has widened them, the V
+                        // rows once every worker has written its part of the image
+                        const int pq = q - TC_NBUF;
+                        const bool was_v = pq > 0 && (pq & 1) == 0;
+                        const int G = g_u + (pq == 0 ? 0 : was_v ? (pq - 2) >> 1 : (pq + 1) >> 1);
+                        TC_T(w0);
+                        tc_wait(was_v ? &p_ready[G & 1] : &kconv[G & 1], (uint32_t) ((G >> 1) & 1), a.status, 7);
+                        TC_T(w1);
+                        TC_ACC(9, w0, w1);
+                    }
+                    TC_T(i0);
+                    const bool is_v = q == 2 * nt_u - 1 || (q > 0 && (q & 1) == 0);
+                    const int tile = q == 0 ? 0 : q == 2 * nt_u - 1 ? nt_u - 1 : is_v ? (q - 2) >> 1 : (q + 1) >> 1;
+                    const int p_t = klo_u + tile * UT;
+                    const int buf = (ib_u + q) & (TC_NBUF - 1);
                     unsigned char * dst = stg + (size_t) buf * BUF;
-                    const CUtensorMap * map = (q & 1) ? &mapV : &mapK;
-                    const int nbox = p_t + TILE < k_hi ? 2 : 1;   // 64-position boxes that hold keys of the run
-                    mbar_expect_tx(&full[buf], (uint32_t) nbox * TILE * HB);
+                    const CUtensorMap * map = is_v ? &mapV : &mapK;
+                    const int nbox = p_t + TILE < khi_u ? 2 : 1;   // 64-position boxes that hold keys of the run
+                    if (lead) mbar_expect_tx(&full[buf], (uint32_t) nbox * TILE * HB);
                     for (int h = 0; h < nbox; ++h) {
                         const int p = p_t + h * TILE;
                         int y = p, z = 0;
                         if (tab) {
-                            const int idx = (p >> a.g.psh) - pg0;
+                            const int idx = (p >> a.g.psh) - pg0_u;
                             z = idx < TC_PGS ? pgs[idx] : tab[p >> a.g.psh];
                             y = p & ((1 << a.g.psh) - 1);
-                            if (z < 0) { atomicOr(a.status, ST_BAD_PAGE); z = 0; }
+                            if (z < 0) { if (lead) atomicOr(a.status, ST_BAD_PAGE); z = 0; }
                         }
-                        tma_box3(dst + h * TILE * HB, map, hk * (HB / 2), y, z, &full[buf]);
+                        if (lead) tma_box3(dst + h * TILE * HB, map, hk * (HB / 2), y, z, &full[buf]);
                     }
-                };
-                issue(0); issue(1); issue(2);
-                constexpr uint32_t id_qk = umma::idesc_f16(UT, NC, false, false);   // S^T[128 x NC] = K (tensor memory) * Q^T (K-major)
-                constexpr uint32_t id_pv = umma::idesc_f16(UT, DH, false, true);    // O[128 x 256] += P (K-major) * V (MN-major)
-                const uint32_t q_s = smem_u32(QI), p_s = smem_u32(PI), v_s = smem_u32(VF);
-                for (int i = 0; i < nt; ++i) {
-                    const uint32_t par = (uint32_t) ((g + i) & 1);
-                    mbar_wait(kconv, par, a.status);       // every worker warp has written its part of K and is done with the K staging
-                    umma::fence_after_sync();
-#pragma unroll
-                    for (int ks = 0; ks < DH / 16; ++ks)
-                        umma::mma_ts(tS, tA + ks * 8, umma::smem_desc(q_s + ks * 2 * (NC * 16), NC * 16, 128), id_qk, ks > 0);
-                    umma::commit(s_full);
-                    issue(2 * i + 3);
-                    mbar_wait(p_ready, par, a.status);     // P and the V image are in place, the V staging is free
-                    umma::fence_after_sync();
-#pragma unroll
-                    for (int ks = 0; ks < UT / 16; ++ks)
-                        umma::mma_ss(tO, umma::smem_desc(p_s + ks * 2 * TC_PLBO, TC_PLBO, 128), umma::smem_desc(v_s + ks * 2 * 4096, 4096, 128),
-                                     id_pv, (i > 0 || ks > 0) ? 1u : 0u);
-                    umma::commit(pv_done);
-                    issue(2 * i + 4);
+                    TC_T(i1);
+                    TC_ACC(11, i0, i1);
                 }
             }
             __syncwarp();
@@ -210,69 +287,91 @@ decode_tc_k(const dec_args a, const __grid_constant__ CUtensorMap mapK, const __
             // ---------------- workers ----------------
             const bool act = gq < a.q_len && gq < NC / 8;           // this warp's columns 8 gq .. 8 gq + 5 hold verify row gq
             const int pos_g = act ? row_pos(a, slot, gq) : -1;
+            const int kk = 32 * lq + lane;                          // this thread's key of the tile in the K and score phases
+            const int vkey = tid & (UT - 1), vb = tid >> 7;         // and its key / first block in the V phase
+            unsigned char * const vdst = VF + vb * 512 + (vkey >> 3) * 4096 + (vkey & 7) * 16;
+            unsigned char * const pdst = PI + gq * 128 + (kk >> 3) * TC_PLBO + (kk & 7) * 2;
+            const float4 * mm4 = reinterpret_cast<const float4 *>(mm) + 4 * gq;
             float l_acc[GQA];
 #pragma unroll
             for (int e = 0; e < GQA; ++e) l_acc[e] = 0.0f;
-            for (int i = 0; i < nt; ++i) {
-                const int gi = g + i, p_t = k_lo + i * UT;
-                // ---- K rows -> tensor memory (lane = key; this warp: blocks 2 gq, 2 gq + 1 of keys 32 lq ..)
-                {
-                    const int qi = 2 * gi, buf = qi % TC_NBUF;
-                    mbar_wait(&full[buf], (uint32_t) ((qi / TC_NBUF) & 1), a.status);
-                    const unsigned char * row = stg + (size_t) buf * BUF + (32 * lq + lane) * HB;
+
+            auto conv_k = [&](int j) {   // K rows of tile j -> tensor memory (lane = key; this warp: blocks 2 gq, 2 gq + 1 of keys 32 lq ..)
+                const int qi = ib + item_k(j), buf = qi & (TC_NBUF - 1), G = g + j;
+                TC_T(k0);
+                tc_wait(&full[buf], (uint32_t) ((qi >> 2) & 1), a.status, 2);
+                TC_T(k1);
+                TC_ACC(0, k0, k1);
+                const unsigned char * row = stg + (size_t) buf * BUF + kk * HB;
 #pragma unroll
-                    for (int bb = 0; bb < 2; ++bb) {
-                        uint32_t r[16];
-                        tc_block<KT>(row, 2 * gq + bb, r);
-                        umma::tmem_st16(tA + lane_off + (2 * gq + bb) * 16, r);
-                    }
-                    umma::tmem_st_wait();
-                    umma::fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) tc_arrive(kconv);
+                for (int bb = 0; bb < 2; ++bb) {
+                    uint32_t r[16];
+                    tc_block<KT>(row, 2 * gq + bb, true, r);
+                    umma::tmem_st16(tA + 128 * (G & 1) + lane_off + (2 * gq + bb) * 16, r);
                 }
+                umma::tmem_st_wait();
+                umma::fence_before_sync();
+                __syncwarp();
+                if (lane == 0) tc_arrive(&kconv[G & 1]);
+                TC_T(k2);
+                TC_ACC(1, k1, k2);
+            };
+
+            conv_k(0);
+            for (int i = 0; i < nt; ++i) {
+                const int G = g + i, p_t = k_lo + i * UT;
+#ifdef TC_PROF
+                long long t_mark = 0;
+#endif
+                if (i + 1 < nt) conv_k(i + 1);
                 // ---- V rows -> f16 image, MN-major: byte(key, d) = (d / 8) * 128 + (key / 8) * 4096 + (key % 8) * 16 + (d % 8) * 2
                 {
-                    const int qi = 2 * gi + 1, buf = qi % TC_NBUF;
-                    mbar_wait(&full[buf], (uint32_t) ((qi / TC_NBUF) & 1), a.status);
-                    if (gi > 0) mbar_wait(pv_done, (uint32_t) ((gi - 1) & 1), a.status);   // the previous P V has read the image and P
-                    const int key = tid & (UT - 1), kb = tid >> 7;
-                    const unsigned char * row = stg + (size_t) buf * BUF + key * HB;
-                    const bool valid = p_t + key < k_hi;   // rows past the run's last key may hold anything: they enter as zeros
+                    const int qi = ib + item_v(i), buf = qi & (TC_NBUF - 1);
+                    TC_T(v0);
+                    tc_wait(&full[buf], (uint32_t) ((qi >> 2) & 1), a.status, 3);
+                    TC_T(v1);
+                    if (G > 0) tc_wait(pv_done, (uint32_t) ((G - 1) & 1), a.status, 4);
+                    TC_T(v2);
+                    TC_ACC(2, v0, v1);
+                    TC_ACC(3, v1, v2);
+                    TC_MARK(t_mark);   // the previous P V has read the image and P
+                    const unsigned char * row = stg + (size_t) buf * BUF + vkey * HB;
+                    const bool valid = p_t + vkey < k_hi;   // rows past the run's last key may hold anything: they enter as zeros
 #pragma unroll
                     for (int u = 0; u < 2; ++u) {
-                        const int blk = kb + 4 * u;
                         uint32_t r[16];
-                        if (valid) tc_block<KT>(row, blk, r);
-                        else {
-#pragma unroll
-                            for (int c = 0; c < 16; ++c) r[c] = 0u;
-                        }
-                        unsigned char * dst = VF + (4 * blk) * 128 + (key >> 3) * 4096 + (key & 7) * 16;
+                        tc_block<KT>(row, vb + 4 * u, valid, r);
 #pragma unroll
                         for (int c = 0; c < 4; ++c)
-                            *reinterpret_cast<uint4 *>(dst + c * 128) = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
+                            *reinterpret_cast<uint4 *>(vdst + u * 2048 + c * 128) = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
                     }
                 }
                 // ---- scores of this thread's key for the six heads of verify row gq
-                mbar_wait(s_full, (uint32_t) (gi & 1), a.status);
+                TC_T(s0_);
+                TC_ACC(4, t_mark, s0_);
+                tc_wait(&s_full[G & 1], (uint32_t) ((G >> 1) & 1), a.status, 5);
+                TC_T(s1_);
+                TC_ACC(5, s0_, s1_);
                 umma::fence_after_sync();
-                float s[GQA];
+                float s[GQA], ofs[GQA];
                 int grow = 0;
                 if (act) {
                     uint32_t sr[8];
-                    umma::tmem_ld8(tS + lane_off + 8 * gq, sr);
+                    umma::tmem_ld8(tS + 32 * (G & 1) + lane_off + 8 * gq, sr);
                     umma::tmem_ld_wait();
-                    const int key_abs = p_t + 32 * lq + lane;
+                    const int key_abs = p_t + kk;
                     const bool masked = key_abs > pos_g || key_abs >= k_hi;
+                    const float4 m0 = mm4[0], m1 = mm4[1], m2 = mm4[2];
+                    const float gap[GQA] = {m0.x, m0.z, m1.x, m1.z, m2.x, m2.z};
+                    ofs[0] = m0.y; ofs[1] = m0.w; ofs[2] = m1.y; ofs[3] = m1.w; ofs[4] = m2.y; ofs[5] = m2.w;
 #pragma unroll
                     for (int e = 0; e < GQA; ++e) {
                         s[e] = masked ? B200_NEG_INF : __uint_as_float(sr[e]);
-                        grow |= s[e] > mref[8 * gq + e] + REF_GAP;
+                        grow |= s[e] > gap[e];
                     }
                 } else {
 #pragma unroll
-                    for (int e = 0; e < GQA; ++e) s[e] = B200_NEG_INF;
+                    for (int e = 0; e < GQA; ++e) { s[e] = B200_NEG_INF; ofs[e] = 0.0f; }
                 }
                 // A column's reference maximum trails its true maximum by at most REF_GAP; it moves (and O, l are rescaled)
                 // only when some key of the tile outgrows it, which the workers find out with one vote per tile.
@@ -292,50 +391,57 @@ decode_tc_k(const dec_args a, const __grid_constant__ CUtensorMap mapK, const __
                         if ((tid >> 3) < a.q_len && (tid & 7) < GQA) {
                             const float mx = fmaxf(fmaxf(wx[tid], wx[32 + tid]), fmaxf(wx[64 + tid], wx[96 + tid]));
                             const float m_old = mref[tid];
-                            if (mx > m_old + REF_GAP) { f = ex2f(m_old - mx); mref[tid] = mx; }   // 2^(-inf) = 0 on the first move
+                            if (mx > m_old + REF_GAP) {   // mx is finite here
+                                f = ex2f(m_old - mx);     // 2^(-inf) = 0 on the first move
+                                mref[tid] = mx;
+                                mm[tid] = make_float2(mx + REF_GAP, mx - PSHIFT);
+                            }
                         }
                         fsc[tid] = f;
                     }
                     tc_bar_workers();
                     if (act) {
+                        const float4 m0 = mm4[0], m1 = mm4[1], m2 = mm4[2];
+                        ofs[0] = m0.y; ofs[1] = m0.w; ofs[2] = m1.y; ofs[3] = m1.w; ofs[4] = m2.y; ofs[5] = m2.w;
 #pragma unroll
                         for (int e = 0; e < GQA; ++e) l_acc[e] *= fsc[8 * gq + e];
                     }
-                    if (lq == 0 && i > 0) {   // O rows live in lanes 0..31: the four warps of lane quarter 0 take 64 columns each
-                        const float f = fsc[lane];
-                        if (__any_sync(0xffffffffu, f != 1.0f)) {
-#pragma unroll 1
-                            for (int h = 0; h < 2; ++h) {
-                                uint32_t o[32];
-                                umma::tmem_ld32(tO + 64 * gq + 32 * h, o);
-                                umma::tmem_ld_wait();
+                    if (i > 0 && o_warp) {   // O^T: lane = dim, column = row; this warp's 16 columns of its half
+                        const float4 * f4 = reinterpret_cast<const float4 *>(fsc) + 4 * cO;
+                        const float4 fa = f4[0], fb = f4[1], fc = f4[2], fd = f4[3];
+                        const float f[16] = {fa.x, fa.y, fa.z, fa.w, fb.x, fb.y, fb.z, fb.w, fc.x, fc.y, fc.z, fc.w, fd.x, fd.y, fd.z, fd.w};
+                        bool any = false;
 #pragma unroll
-                                for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * f);
-                                umma::tmem_st32(tO + 64 * gq + 32 * h, o);
-                            }
+                        for (int c = 0; c < 16; ++c) any = any || f[c] != 1.0f;
+                        if (any) {
+                            uint32_t o[16];
+                            umma::tmem_ld16(tO + lane_off + hO * NC + 16 * cO, o);
+                            umma::tmem_ld_wait();
+#pragma unroll
+                            for (int c = 0; c < 16; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * f[c]);
+                            umma::tmem_st16(tO + lane_off + hO * NC + 16 * cO, o);
                             umma::tmem_st_wait();
                         }
                     }
                 }
-                // ---- P = 2^(S - reference + 8) as f16 into the K-major A image: byte(row, key) = (row / 8) * 128 + (key / 8) * TC_PLBO + (row % 8) * 16 + (key % 8) * 2
+                // ---- P = 2^(S - reference + 8) as f16 into the K-major image: byte(row, key) = (row / 8) * 128 + (key / 8) * TC_PLBO + (row % 8) * 16 + (key % 8) * 2
                 if (act) {
-                    const int kk = 32 * lq + lane;
-                    unsigned char * pd = PI + gq * 128 + (kk >> 3) * TC_PLBO + (kk & 7) * 2;
 #pragma unroll
                     for (int e = 0; e < GQA; ++e) {
-                        const float m = mref[8 * gq + e];
-                        const __half p = __float2half_rn(ex2f(s[e] - (m == B200_NEG_INF ? 0.0f : m) + PSHIFT));
-                        l_acc[e] += __half2float(p);
-                        *reinterpret_cast<__half *>(pd + e * 16) = p;
+                        const float p = ex2f(s[e] - ofs[e]);
+                        l_acc[e] += p;
+                        *reinterpret_cast<__half *>(pdst + e * 16) = __float2half_rn(p);
                     }
                 }
                 umma::fence_async_smem();
                 umma::fence_before_sync();
                 __syncwarp();
-                if (lane == 0) tc_arrive(p_ready);
+                if (lane == 0) tc_arrive(&p_ready[G & 1]);
+                TC_T(s2_);
+                TC_ACC(6, s1_, s2_);
             }
             // ---------------- the run's partial (O, reference maximum, sum) ----------------
-            mbar_wait(pv_done, (uint32_t) ((g + nt - 1) & 1), a.status);
+            tc_wait(pv_done, (uint32_t) ((g + nt - 1) & 1), a.status, 6);
             umma::fence_after_sync();
             if (act) {
 #pragma unroll
@@ -352,21 +458,15 @@ decode_tc_k(const dec_args a, const __grid_constant__ CUtensorMap mapK, const __
                 a.pm[unit * R + r] = mref[tid];
                 a.pl[unit * R + r] = (wx[tid] + wx[32 + tid]) + (wx[64 + tid] + wx[96 + tid]);
             }
-            if (lq == 0) {
-                const bool live = (lane >> 3) < a.q_len && (lane & 7) < GQA;
-                const int r = (lane >> 3) * GQA + (lane & 7);
-#pragma unroll 1
-                for (int h = 0; h < 2; ++h) {
-                    uint32_t o[32];
-                    umma::tmem_ld32(tO + 64 * gq + 32 * h, o);
-                    umma::tmem_ld_wait();
-                    if (live) {
-                        float4 * dst = reinterpret_cast<float4 *>(a.po + (unit * R + r) * DH + 64 * gq + 32 * h);
+            if (o_warp) {
+                uint32_t o[16];
+                umma::tmem_ld16(tO + lane_off + hO * NC + 16 * cO, o);
+                umma::tmem_ld_wait();
+                float * dst = a.po + unit * R * DH + 128 * hO + kk;
 #pragma unroll
-                        for (int c = 0; c < 8; ++c)
-                            dst[c] = make_float4(__uint_as_float(o[4 * c]), __uint_as_float(o[4 * c + 1]), __uint_as_float(o[4 * c + 2]),
-                                                 __uint_as_float(o[4 * c + 3]));
-                    }
+                for (int c = 0; c < 16; ++c) {
+                    const int col = 16 * cO + c, jg = col >> 3, hh = col & 7;
+                    if (jg < a.q_len && hh < GQA) dst[(size_t) (jg * GQA + hh) * DH] = __uint_as_float(o[c]);
                 }
             }
             umma::fence_before_sync();

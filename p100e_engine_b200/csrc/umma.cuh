@@ -35,6 +35,13 @@ __host__ __device__ constexpr uint32_t idesc_f16(int M, int N, bool a_mn, bool b
            | ((uint32_t) (N >> 3) << 17) | ((uint32_t) (M >> 4) << 24);
 }
 
+// true in exactly one lane of a fully active warp
+__device__ __forceinline__ bool elect_one() {
+    uint32_t p;
+    asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(p));
+    return p != 0;
+}
+
 // ---- tensor memory ----
 // One full warp allocates `cols` (power of two, 32..512) columns and publishes the base address in shared memory.
 __device__ __forceinline__ void tmem_alloc(uint32_t * smem_out, uint32_t cols) {
