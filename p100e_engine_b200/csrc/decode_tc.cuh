@@ -32,9 +32,13 @@ template <uint32_t KT> constexpr size_t tc_smem_bytes() { return TC_HDR + (size_
 __device__ __forceinline__ void tc_arrive(uint64_t * bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-// a wait that records which one gave up (bits 8.. of the status word, beside ST_WAIT_TIMEOUT)
-__device__ __forceinline__ void tc_wait(uint64_t * bar, uint32_t parity, unsigned * status, int site) {
+// A wait that records which one gave up (bits 8.. of the status word, beside ST_WAIT_TIMEOUT).  The first probe is inline
+// (the hardware suspends the thread inside it for a while); only a probe that fails enters the timed loop, out of line.
+__device__ __noinline__ void tc_wait_slow(uint64_t * bar, uint32_t parity, unsigned * status, int site) {
     if (!mbar_wait(bar, parity, status)) atomicOr(status, 0x100u << site);
+}
+__device__ __forceinline__ void tc_wait(uint64_t * bar, uint32_t parity, unsigned * status, int site) {
+    if (!mbar_try_wait(bar, parity)) tc_wait_slow(bar, parity, status, site);
 }
 #ifdef TC_PROF
 __device__ unsigned long long g_tc_prof[16];
@@ -55,14 +59,12 @@ __device__ __forceinline__ int tc_vote_workers(int v) {
 }
 
 // One 32-value block of a cache row -> 16 registers of f16 pairs (register m = dims 2m, 2m+1 of the block), each value the
-// rounded product of the stored integer and the block's f16 scale.  live = false gives zeros whatever the bytes are (the
-// integer part is finite for every bit pattern; only the scale is replaced).
+// rounded product of the stored integer and the block's f16 scale, given as the pair d2 (q8_0; d2 = 0 gives zeros whatever
+// the bytes are: the integer part is finite for every bit pattern) or read from the block (q4_0; live = false gives zeros).
 template <uint32_t KT>
-__device__ __forceinline__ void tc_block(const unsigned char * row, int blk, bool live, uint32_t (&r)[16]) {
+__device__ __forceinline__ void tc_block(const unsigned char * row, int blk, uint32_t d2, bool live, uint32_t (&r)[16]) {
     if constexpr (KT == B200_KV_Q8_0) {
         const uint4 a = *reinterpret_cast<const uint4 *>(row + 16 + 32 * blk), b = *reinterpret_cast<const uint4 *>(row + 32 + 32 * blk);
-        const uint32_t sc = live ? *reinterpret_cast<const uint16_t *>(row + 2 * blk) : 0u;
-        const uint32_t d2 = __byte_perm(sc, sc, 0x1010);
         const uint32_t wv[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -85,14 +87,14 @@ __device__ __forceinline__ void tc_block(const unsigned char * row, int blk, boo
             q[0] = p[1]; q[1] = p[2]; q[2] = p[3]; q[3] = p[4];
         }
         if (!live) sc = 0u;
-        const uint32_t d2 = __byte_perm(sc, sc, 0x1010);
+        const uint32_t dq = __byte_perm(sc, sc, 0x1010);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const uint32_t lo = q[j] & 0x0f0f0f0fu, hi = (q[j] >> 4) & 0x0f0f0f0fu;
-            r[2 * j] = hmul2_u32(cvt_n4x2<0>(lo), d2);
-            r[2 * j + 1] = hmul2_u32(cvt_n4x2<1>(lo), d2);
-            r[8 + 2 * j] = hmul2_u32(cvt_n4x2<0>(hi), d2);
-            r[8 + 2 * j + 1] = hmul2_u32(cvt_n4x2<1>(hi), d2);
+            r[2 * j] = hmul2_u32(cvt_n4x2<0>(lo), dq);
+            r[2 * j + 1] = hmul2_u32(cvt_n4x2<1>(lo), dq);
+            r[8 + 2 * j] = hmul2_u32(cvt_n4x2<0>(hi), dq);
+            r[8 + 2 * j + 1] = hmul2_u32(cvt_n4x2<1>(hi), dq);
         }
     }
 }
@@ -166,10 +168,6 @@ decode_tc_k(const dec_args a, const __grid_constant__ CUtensorMap mapK, const __
         const int32_t * tab = a.g.pt ? a.g.pt + (a.g.rtab ? a.g.rtab[slot * a.q_len] : 0) : nullptr;
         const int pg0 = tab ? k_lo >> a.g.psh : 0;
         const int ib = 2 * g;
-        // staging item of a tile's K rows / V rows in consumption order: K0, K1, V0, K2, V1, .., K(nt-1), V(nt-2), V(nt-1)
-        auto item_k = [&](int j) { return j == 0 ? 0 : 2 * j - 1; };
-        auto item_v = [&](int j) { return j < nt - 1 ? 2 * j + 2 : 2 * nt - 1; };
-
         if (worker) {
             if (tab) {
                 const int npg = min(TC_PGS, ((k_hi - 1) >> a.g.psh) - pg0 + 1);
@@ -289,86 +287,108 @@ decode_tc_k(const dec_args a, const __grid_constant__ CUtensorMap mapK, const __
             const int pos_g = act ? row_pos(a, slot, gq) : -1;
             const int kk = 32 * lq + lane;                          // this thread's key of the tile in the K and score phases
             const int vkey = tid & (UT - 1), vb = tid >> 7;         // and its key / first block in the V phase
+            const unsigned char * const krow0 = stg + kk * HB, * const vrow0 = stg + vkey * HB;
             unsigned char * const vdst = VF + vb * 512 + (vkey >> 3) * 4096 + (vkey & 7) * 16;
             unsigned char * const pdst = PI + gq * 128 + (kk >> 3) * TC_PLBO + (kk & 7) * 2;
             const float4 * mm4 = reinterpret_cast<const float4 *>(mm) + 4 * gq;
             float l_acc[GQA];
 #pragma unroll
             for (int e = 0; e < GQA; ++e) l_acc[e] = 0.0f;
+            int cons = ib;   // staging items are consumed in ring order: K0, K1, V0, K2, V1, ..
 
-            auto conv_k = [&](int j) {   // K rows of tile j -> tensor memory (lane = key; this warp: blocks 2 gq, 2 gq + 1 of keys 32 lq ..)
-                const int qi = ib + item_k(j), buf = qi & (TC_NBUF - 1), G = g + j;
+            // K rows of a tile -> tensor-memory buffer tb_k (lane = key; this warp: blocks 2 gq, 2 gq + 1 of keys 32 lq ..).
+            // The stores are left in flight: k_publish waits for them and tells the issuers.
+            auto k_store = [&](int G) {
+                const int buf = cons & (TC_NBUF - 1);
                 TC_T(k0);
-                tc_wait(&full[buf], (uint32_t) ((qi >> 2) & 1), a.status, 2);
+                tc_wait(&full[buf], (uint32_t) ((cons >> 2) & 1), a.status, 2);
                 TC_T(k1);
                 TC_ACC(0, k0, k1);
-                const unsigned char * row = stg + (size_t) buf * BUF + kk * HB;
+                ++cons;
+                const unsigned char * row = krow0 + buf * BUF;
+                uint32_t sc2 = 0;
+                if constexpr (KT == B200_KV_Q8_0) sc2 = *reinterpret_cast<const uint32_t *>(row + 4 * gq);   // the two blocks' scales
 #pragma unroll
                 for (int bb = 0; bb < 2; ++bb) {
                     uint32_t r[16];
-                    tc_block<KT>(row, 2 * gq + bb, true, r);
+                    tc_block<KT>(row, 2 * gq + bb, __byte_perm(sc2, sc2, bb ? 0x3232 : 0x1010), true, r);
                     umma::tmem_st16(tA + 128 * (G & 1) + lane_off + (2 * gq + bb) * 16, r);
                 }
+                TC_T(k2);
+                TC_ACC(1, k1, k2);
+            };
+            auto k_publish = [&](int G) {
                 umma::tmem_st_wait();
                 umma::fence_before_sync();
                 __syncwarp();
                 if (lane == 0) tc_arrive(&kconv[G & 1]);
-                TC_T(k2);
-                TC_ACC(1, k1, k2);
             };
 
-            conv_k(0);
+            k_store(g);
+            k_publish(g);
             for (int i = 0; i < nt; ++i) {
                 const int G = g + i, p_t = k_lo + i * UT;
 #ifdef TC_PROF
                 long long t_mark = 0;
 #endif
-                if (i + 1 < nt) conv_k(i + 1);
+                if (i + 1 < nt) k_store(G + 1);
+                // ---- this tile's scores: the load from tensor memory flies during the V phase
+                TC_T(s0_);
+                tc_wait(&s_full[G & 1], (uint32_t) ((G >> 1) & 1), a.status, 5);
+                TC_T(s1_);
+                TC_ACC(5, s0_, s1_);
+                umma::fence_after_sync();
+                uint32_t sr[8];
+                if (act) umma::tmem_ld8(tS + 32 * (G & 1) + lane_off + 8 * gq, sr);
                 // ---- V rows -> f16 image, MN-major: byte(key, d) = (d / 8) * 128 + (key / 8) * 4096 + (key % 8) * 16 + (d % 8) * 2
                 {
-                    const int qi = ib + item_v(i), buf = qi & (TC_NBUF - 1);
+                    const int buf = cons & (TC_NBUF - 1);
                     TC_T(v0);
-                    tc_wait(&full[buf], (uint32_t) ((qi >> 2) & 1), a.status, 3);
+                    tc_wait(&full[buf], (uint32_t) ((cons >> 2) & 1), a.status, 3);
                     TC_T(v1);
-                    if (G > 0) tc_wait(pv_done, (uint32_t) ((G - 1) & 1), a.status, 4);
+                    if (G > 0) tc_wait(pv_done, (uint32_t) ((G - 1) & 1), a.status, 4);   // the previous P V has read the image and P
                     TC_T(v2);
                     TC_ACC(2, v0, v1);
                     TC_ACC(3, v1, v2);
-                    TC_MARK(t_mark);   // the previous P V has read the image and P
-                    const unsigned char * row = stg + (size_t) buf * BUF + vkey * HB;
+                    TC_MARK(t_mark);
+                    ++cons;
+                    const unsigned char * row = vrow0 + buf * BUF;
                     const bool valid = p_t + vkey < k_hi;   // rows past the run's last key may hold anything: they enter as zeros
 #pragma unroll
                     for (int u = 0; u < 2; ++u) {
-                        uint32_t r[16];
-                        tc_block<KT>(row, vb + 4 * u, valid, r);
+                        uint32_t r[16], d2 = 0;
+                        if constexpr (KT == B200_KV_Q8_0) {
+                            const uint32_t sc = valid ? *reinterpret_cast<const uint16_t *>(row + 2 * (vb + 4 * u)) : 0u;
+                            d2 = __byte_perm(sc, sc, 0x1010);
+                        }
+                        tc_block<KT>(row, vb + 4 * u, d2, valid, r);
 #pragma unroll
                         for (int c = 0; c < 4; ++c)
                             *reinterpret_cast<uint4 *>(vdst + u * 2048 + c * 128) = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
                     }
                 }
+                TC_T(s2_);
+                TC_ACC(4, t_mark, s2_);
+                if (i + 1 < nt) k_publish(G + 1);
                 // ---- scores of this thread's key for the six heads of verify row gq
-                TC_T(s0_);
-                TC_ACC(4, t_mark, s0_);
-                tc_wait(&s_full[G & 1], (uint32_t) ((G >> 1) & 1), a.status, 5);
-                TC_T(s1_);
-                TC_ACC(5, s0_, s1_);
-                umma::fence_after_sync();
                 float s[GQA], ofs[GQA];
                 int grow = 0;
                 if (act) {
-                    uint32_t sr[8];
-                    umma::tmem_ld8(tS + 32 * (G & 1) + lane_off + 8 * gq, sr);
                     umma::tmem_ld_wait();
-                    const int key_abs = p_t + kk;
-                    const bool masked = key_abs > pos_g || key_abs >= k_hi;
                     const float4 m0 = mm4[0], m1 = mm4[1], m2 = mm4[2];
                     const float gap[GQA] = {m0.x, m0.z, m1.x, m1.z, m2.x, m2.z};
                     ofs[0] = m0.y; ofs[1] = m0.w; ofs[2] = m1.y; ofs[3] = m1.w; ofs[4] = m2.y; ofs[5] = m2.w;
 #pragma unroll
-                    for (int e = 0; e < GQA; ++e) {
-                        s[e] = masked ? B200_NEG_INF : __uint_as_float(sr[e]);
-                        grow |= s[e] > gap[e];
+                    for (int e = 0; e < GQA; ++e) s[e] = __uint_as_float(sr[e]);
+                    if (p_t + UT - 1 > pos_g || p_t + UT > k_hi) {   // only tiles that reach past the row's last key or the run's end
+                        const int key_abs = p_t + kk;
+                        if (key_abs > pos_g || key_abs >= k_hi) {
+#pragma unroll
+                            for (int e = 0; e < GQA; ++e) s[e] = B200_NEG_INF;
+                        }
                     }
+#pragma unroll
+                    for (int e = 0; e < GQA; ++e) grow |= s[e] > gap[e];
                 } else {
 #pragma unroll
                     for (int e = 0; e < GQA; ++e) { s[e] = B200_NEG_INF; ofs[e] = 0.0f; }
@@ -437,8 +457,8 @@ decode_tc_k(const dec_args a, const __grid_constant__ CUtensorMap mapK, const __
                 umma::fence_before_sync();
                 __syncwarp();
                 if (lane == 0) tc_arrive(&p_ready[G & 1]);
-                TC_T(s2_);
-                TC_ACC(6, s1_, s2_);
+                TC_T(s3_);
+                TC_ACC(6, s2_, s3_);
             }
             // ---------------- the run's partial (O, reference maximum, sum) ----------------
             tc_wait(pv_done, (uint32_t) ((g + nt - 1) & 1), a.status, 6);
