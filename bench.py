@@ -516,7 +516,7 @@ class Workload:
         """per-layer device times of the step's parts from CUDA events on this rank (eager launches, the slots in one batch, no
         overlap between parts), and the host's time to issue a layer"""
         torch, fast = self.torch, self.fast
-        names = ["attn_prep", "work list + decode_part_k + chunk merge"]
+        names = ["attn_prep", "split plan / work list + attention kernel + merge of the partials"]
         if self.merge is not None:
             import torch.distributed as dist
             from p100e_engine_b200 import dist as Dm
@@ -672,7 +672,10 @@ def run_b200(args):
     peaks = measured_peaks()
     peak = float(peaks.get("hbm_gbs", 6650.0))
     achieved = wl.kv_bytes_layer / (att_ms_avg * 1e-3) / 1e9
-    tr = traffic_ratios().get("decode_part_k", {})
+    # the attention kernel of this call: the even split of a q8_0 verify batch runs on the tcgen05 kernel
+    tc = bool(L.load().b200_attn_dec_tc()) and args.chunk < 0 and wl.slots > 1 and wl.kt == KV_TYPES["q8_0"] and wl.q_len >= 2
+    kname = "decode_tc_k" if tc else "decode_part_k"
+    tr = traffic_ratios().get(kname, {})
     line = base_line(args, wl.slots, wl.q_len, wl.layers)
     line["config"].update({"parallelism": "kv-head shards %d x sequence shards %d" % (plan.n_head_shards, plan.n_seq),
                            "keys_per_layer": int(wl.n_ctx.sum()), "chunk_keys": args.chunk,
@@ -682,7 +685,7 @@ def run_b200(args):
                  "clocks": clocks, "gpu_launches": int(launches), "out_fingerprint": fingerprint,
                  "e2e": {"value": total_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
                          "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
-                 "roofline": {"bound": "hbm", "kernel": "decode_part_k (+ work list, chunk merge) per layer call", "achieved": achieved,
+                 "roofline": {"bound": "hbm", "kernel": kname + " (+ split plan / work list, merge of the partials) per layer call", "achieved": achieved,
                               "peak": peak, "peak_source": "measured" if peaks else "fallback", "unit": "GB/s",
                               "frac": achieved / peak,
                               "traffic": int(tr["dram_bytes_per_kv_byte"] * wl.kv_bytes_layer) if tr else None,

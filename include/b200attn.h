@@ -142,11 +142,12 @@ void b200_attn_dec2_set_nsplit(int n);
 int b200_attn_dec2_reload_env(void);
 int b200_attn_chunk_keys(void);        /* the smallest default chunk (keys): B200ATTN_CHUNK or 512 */
 int b200_attn_fixed_chunk(int n_ctx);  /* the chunk the entry points above use for a cache of n_ctx positions */
-/* Kernel choice of the batched entry points with chunk_keys = -1 (even split of the batch): quantised caches whose tiles
- * can be fetched through tensor maps (pages of at least 64 positions) run on the tcgen05 kernel (one CTA per SM, K widened
- * into tensor memory, V into an f16 image in shared memory); everything else on the mma.sync kernel.  set_tc(0) keeps
- * the mma.sync kernel everywhere, set_tc(1) restores the default, set_tc(-1) re-reads B200ATTN_TC (0 = off); tc() reports
- * the setting.  Both kernels meet the same tolerance; their results are not bitwise equal. */
+/* Kernel choice of the batched entry points with chunk_keys = -1 (even split of the batch): q8_0 caches whose tiles can be
+ * fetched through tensor maps (pages of at least 64 positions), with two to four rows per slot, run on the tcgen05 kernel
+ * (one CTA per SM, K widened into tensor memory, V into an f16 image in shared memory); everything else on the mma.sync
+ * kernel.  set_tc(0) keeps the mma.sync kernel everywhere, set_tc(1) restores the default, set_tc(-1) re-reads
+ * B200ATTN_TC (0 = off); tc() reports the setting.  Both kernels meet the same tolerance; their results are not bitwise
+ * equal. */
 int b200_attn_dec_tc(void);
 void b200_attn_dec_set_tc(int on);
 

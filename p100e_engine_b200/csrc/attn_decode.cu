@@ -1172,40 +1172,41 @@ bool cache_tiles(const kv_view & g, int n_ctx) {
     return (!g.pt || g.psh >= 6) && g.rowb % 16 == 0 &&
            (g.pt ? g.pstride < ((unsigned long long) 1 << 40) : (n_ctx >= 1 && g.rowb * (unsigned long long) n_ctx < ((unsigned long long) 1 << 40)));
 }
-// The tensor-core kernel serves the even split of quantised caches that can be tiled; B200ATTN_TC=0 keeps the mma.sync kernel.
+// The tensor-core kernel serves the even split of q8_0 caches that can be tiled, for two to four rows per slot (one row
+// per slot and q4_0 are faster on the mma.sync kernel: their tiles cost fewer instructions there); B200ATTN_TC=0 keeps the
+// mma.sync kernel everywhere.
 int g_tc = -1;   // -1 = not read yet
 bool tc_enabled() {
     if (g_tc < 0) { const char * e = getenv("B200ATTN_TC"); g_tc = (e && *e == '0') ? 0 : 1; }
     return g_tc != 0;
 }
-bool tc_eligible(const b200_kv_cache & c) {
-    return tc_enabled() && c.type != B200_KV_F16 && cache_tiles(view_of(c), c.n_ctx) && tensor_map_encoder() != nullptr;
+bool tc_eligible(const b200_kv_cache & c, int q_len) {
+    return tc_enabled() && c.type == B200_KV_Q8_0 && q_len >= 2 && cache_tiles(view_of(c), c.n_ctx) && tensor_map_encoder() != nullptr;
 }
 
-template <uint32_t KT, int NC>
+template <int NC>
 int launch_tc(const dec_args & a_in, unsigned blocks, cudaStream_t s) {
     dec_args a = a_in;
     CUtensorMap mapK, mapV;
     memset(&mapK, 0, sizeof mapK);
     memset(&mapV, 0, sizeof mapV);
-    if (!make_cache_map(&mapK, a.g.k, a, traits<KT>::HB) || !make_cache_map(&mapV, a.g.v, a, traits<KT>::HB))
+    if (!make_cache_map(&mapK, a.g.k, a, TC_HB) || !make_cache_map(&mapV, a.g.v, a, TC_HB))
         B200_REFUSE(B200_ERR_CUDA, "attn_decode: the cache's tensor map could not be encoded");
     a.tiled = 1;
-    const size_t sm = tc_smem_bytes<KT>();
+    const size_t sm = tc_smem_bytes();
     static std::atomic<bool> attr_done[64];
     int dev = 0;
     cudaGetDevice(&dev);
     if (!attr_done[dev & 63].load(std::memory_order_acquire)) {
-        if (cudaFuncSetAttribute(decode_tc_k<KT, NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) sm) != cudaSuccess)
+        if (cudaFuncSetAttribute(decode_tc_k<NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) sm) != cudaSuccess)
             return launch_status("attn_decode (shared memory attribute)");
         attr_done[dev & 63].store(true, std::memory_order_release);
     }
-    decode_tc_k<KT, NC><<<blocks, TC_THR, sm, s>>>(a, mapK, mapV);
+    decode_tc_k<NC><<<blocks, TC_THR, sm, s>>>(a, mapK, mapV);
     return B200_OK;
 }
-template <uint32_t KT>
 int launch_tc_nc(const dec_args & a, unsigned blocks, cudaStream_t s) {
-    return a.q_len <= 2 ? launch_tc<KT, 16>(a, blocks, s) : launch_tc<KT, 32>(a, blocks, s);
+    return a.q_len <= 2 ? launch_tc<16>(a, blocks, s) : launch_tc<32>(a, blocks, s);
 }
 
 int sm_count() {
@@ -1253,7 +1254,7 @@ bool decode_geometry(dec_geom & g, uint32_t type, int n_slots, int q_len, int ma
     if (g.split) {
         g.CH = TILE;
         g.max_chunks = (max_n + TILE - 1) / TILE;
-        g.tc = tc && type != B200_KV_F16;   // the tensor-core kernel: one CTA per SM
+        g.tc = tc && type == B200_KV_Q8_0 && q_len >= 2;   // the tensor-core kernel: one CTA per SM
         g.max_cta = std::max(1, std::min(SPLIT_MAX_CTA, (g.tc ? sm_count() : resident_ctas(type, q_len)) / Hkv));
         const size_t nseg = (size_t) g.max_cta + n_slots;
         g.units = nseg * Hkv;
@@ -1323,7 +1324,7 @@ int decode_launch(const float * q, const b200_kv_cache * c, const merge_out & mo
         ++launches;
     }
     int rc;
-    if (gm.split && gm.tc) rc = c->type == B200_KV_Q8_0 ? launch_tc_nc<B200_KV_Q8_0>(a, blocks, s) : launch_tc_nc<B200_KV_Q4_0>(a, blocks, s);
+    if (gm.split && gm.tc) rc = launch_tc_nc(a, blocks, s);
     else if (c->type == B200_KV_F16) rc = launch_part_nt<B200_KV_F16>(a, blocks, s);
     else if (c->type == B200_KV_Q8_0) rc = launch_part_nt<B200_KV_Q8_0>(a, blocks, s);
     else rc = launch_part_nt<B200_KV_Q4_0>(a, blocks, s);
@@ -1344,7 +1345,7 @@ int decode_impl(const float * q, const b200_kv_cache * c, const merge_out & mo, 
     if (chk != B200_OK) return chk;
     if (mo.qbuf && (!mo.out || ((uintptr_t) mo.qbuf & 3))) B200_REFUSE(B200_ERR_SHAPE, "%s: the a16 buffer needs out and 4-byte alignment", who);
     dec_geom gm;
-    if (!decode_geometry(gm, c->type, n_slots, q_len, max_n, c->n_ctx, c->Hkv, chunk_keys, tc_eligible(*c))) B200_REFUSE(B200_ERR_SHAPE, "%s: too many chunks", who);
+    if (!decode_geometry(gm, c->type, n_slots, q_len, max_n, c->n_ctx, c->Hkv, chunk_keys, tc_eligible(*c, q_len))) B200_REFUSE(B200_ERR_SHAPE, "%s: too many chunks", who);
     const size_t need = gm.part_floats + gm.list_ints;
     float * scr = scratch_for(s, need, hint_floats);
     if (!scr) B200_REFUSE(B200_ERR_ALLOC, "%s: split scratch (%zu floats) could not be allocated", who, need);
@@ -1396,7 +1397,7 @@ int decode_noalloc_impl(const float * q, const b200_kv_cache * c, float * out, c
     const int chk = decode_check(q, c, out, gate, n_slots, q_len, Hq, who);
     if (chk != B200_OK) return chk;
     dec_geom gm;
-    const bool ok = decode_geometry(gm, c->type, n_slots, q_len, max_n, c->n_ctx, c->Hkv, chunk_keys, tc_eligible(*c));
+    const bool ok = decode_geometry(gm, c->type, n_slots, q_len, max_n, c->n_ctx, c->Hkv, chunk_keys, tc_eligible(*c, q_len));
     const size_t need = ok ? gm.part_floats + gm.list_ints : 0;
     if (!ok || need > NOALLOC_FLOATS)
         B200_REFUSE(B200_ERR_SCRATCH, "%s: %zu bytes of split partials needed (slots %d x kv heads %d x chunks %d x rows %d), the built-in array holds %zu; "
@@ -1441,13 +1442,6 @@ int b200_attn_dec2_nsplit(int Hkv) {
     return g_nsplit_override > 0 ? g_nsplit_override : MAX_DEFAULT_CHUNKS;
 }
 void b200_attn_dec2_set_nsplit(int n) { g_nsplit_override = n > 0 ? n : 0; }
-#ifdef TC_PROF
-int b200_debug_tc_prof(unsigned long long * out, int reset) {
-    if (out && cudaMemcpyFromSymbol(out, g_tc_prof, sizeof(unsigned long long) * 16) != cudaSuccess) return B200_ERR_CUDA;
-    if (reset) { unsigned long long z[16] = {0}; cudaMemcpyToSymbol(g_tc_prof, z, sizeof z); }
-    return B200_OK;
-}
-#endif
 int b200_attn_dec_tc(void) { return tc_enabled() ? 1 : 0; }
 void b200_attn_dec_set_tc(int on) { g_tc = on < 0 ? -1 : on ? 1 : 0; }
 int b200_attn_dec2_reload_env(void) {

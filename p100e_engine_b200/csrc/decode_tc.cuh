@@ -1,19 +1,27 @@
-// Batched decode / verify on the 5th-generation tensor cores (tcgen05), for quantised caches and the even split of a
-// batch over the SMs.  Included by attn_decode.cu inside its namespace (dec_args, traits, the tensor maps and the split
+// Batched verify (two to four rows per slot) on the 5th-generation tensor cores (tcgen05), for q8_0 caches and the even
+// split of a batch over the SMs.  Included by attn_decode.cu inside its namespace (dec_args, traits, the tensor maps and the split
 // plan are defined there).
 //
 // One CTA per SM walks its run of keys in tiles of 128.  Per tile and kv head:
-//   K rows (TMA -> staging) --16 worker warps: int8 / nibble -> f16 * block scale--> tensor memory, lane = key
+//   K rows (TMA -> staging) --16 worker warps: int8 -> f16 * block scale--> tensor memory, lane = key
 //   S^T[128 keys x rows]   = K (A operand in tensor memory) * Q^T (B operand, K-major image in shared memory)
 //   V rows (TMA -> staging) --workers--> f16 image [key][dim] in shared memory
 //   workers: S^T -> mask -> P = 2^(S - reference maximum + 8) as f16 -> P image [row][key] in shared memory
 //   O^T[256 dims x rows]  += V^T (A operand, the MN-major image, two halves of 128 dims) * P^T (B operand, K-major image)
-// The MMAs and the TMA copies are issued by one thread of a 17th warp; the workers meet it through mbarriers only, and each
-// other once per tile (the vote on "some score outgrew its reference maximum").  K and S^T are double-buffered in tensor
-// memory: the workers widen the K rows of tile i + 1 before they turn to V and the scores of tile i, so the Q K^T of a tile
-// has a whole conversion phase to finish.  Against the mma.sync kernel this takes the multiply-adds, the fragment
-// shuffling and the per-tile accumulator traffic out of the instruction stream: what the CUDA cores still do is the
-// widening of 2 x 128 x 256 cache values per tile and 128 x rows exponentials.
+// Two more warps issue: warp 16 the MMAs, warp 17 the TMA copies (a TMA instruction can hold its thread while the copy
+// unit's queue is full, which must not delay an MMA).  Both walk their loops with all 32 lanes and let one elected lane
+// issue, so that tensor-memory addresses and descriptors are warp-uniform values: the MMA and TMA instructions take their
+// operands from uniform registers, and an issuer that ran as a single diverged lane spent most of a tile moving operands.
+// The workers meet the issuers through mbarriers only, and each other once per tile (the vote on "some score outgrew its
+// reference maximum").  K and S^T are double-buffered in tensor memory: in iteration i the workers widen the K rows of
+// tile i + 1, start the load of tile i's scores from tensor memory, write tile i's V image, then publish K(i + 1) (its
+// tensor-memory stores have landed by then) and turn to the scores: the Q K^T of a tile has a whole conversion phase to
+// finish, and neither tensor-memory latency is waited for.  Barriers that a waiter could fall two phases behind on exist
+// once per buffer (parity alone cannot tell phase n from phase n + 2).
+//
+// Against the mma.sync kernel this takes the multiply-adds, the fragment shuffling and the per-tile accumulator traffic out
+// of the instruction stream: what the CUDA cores still do is the widening of 2 x 128 x 256 cache values per tile (seven
+// instructions per four values) and 128 x rows exponentials.
 //
 // Every wait is bounded (mbar_wait gives up after two seconds and records ST_WAIT_TIMEOUT).
 
@@ -27,7 +35,8 @@ constexpr int TC_QI = 32 * 32 * 16;           // f16 image of up to 32 query row
 constexpr int TC_PLBO = 528;                  // bytes between the 8-key chunks of the P image (512 + 16: stores of a warp spread over the banks)
 constexpr int TC_PI = 8704;                   // P image: 16 chunks of up to 32 rows
 
-template <uint32_t KT> constexpr size_t tc_smem_bytes() { return TC_HDR + (size_t) TC_NBUF * UT * traits<KT>::HB + TC_VF + TC_QI + TC_PI; }
+constexpr int TC_HB = head_bytes(B200_KV_Q8_0);   // the kernel serves q8_0 rows: 8 f16 block scales, then 256 int8
+constexpr size_t tc_smem_bytes() { return TC_HDR + (size_t) TC_NBUF * UT * TC_HB + TC_VF + TC_QI + TC_PI; }
 
 __device__ __forceinline__ void tc_arrive(uint64_t * bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -40,16 +49,6 @@ __device__ __noinline__ void tc_wait_slow(uint64_t * bar, uint32_t parity, unsig
 __device__ __forceinline__ void tc_wait(uint64_t * bar, uint32_t parity, unsigned * status, int site) {
     if (!mbar_try_wait(bar, parity)) tc_wait_slow(bar, parity, status, site);
 }
-#ifdef TC_PROF
-__device__ unsigned long long g_tc_prof[16];
-#define TC_T(v) const long long v = clock64()
-#define TC_MARK(v) v = clock64()
-#define TC_ACC(slot, t0, t1) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (threadIdx.x == 0 || threadIdx.x >= TC_WORKERS)) atomicAdd(&g_tc_prof[slot], (unsigned long long) ((t1) - (t0))); } while (0)
-#else
-#define TC_T(v)
-#define TC_MARK(v)
-#define TC_ACC(slot, t0, t1)
-#endif
 __device__ __forceinline__ void tc_bar_workers() { asm volatile("bar.sync 1, %0;" ::"n"(TC_WORKERS) : "memory"); }
 __device__ __forceinline__ int tc_vote_workers(int v) {
     int r;
@@ -58,54 +57,27 @@ __device__ __forceinline__ int tc_vote_workers(int v) {
     return r;
 }
 
-// One 32-value block of a cache row -> 16 registers of f16 pairs (register m = dims 2m, 2m+1 of the block), each value the
-// rounded product of the stored integer and the block's f16 scale, given as the pair d2 (q8_0; d2 = 0 gives zeros whatever
-// the bytes are: the integer part is finite for every bit pattern) or read from the block (q4_0; live = false gives zeros).
-template <uint32_t KT>
-__device__ __forceinline__ void tc_block(const unsigned char * row, int blk, uint32_t d2, bool live, uint32_t (&r)[16]) {
-    if constexpr (KT == B200_KV_Q8_0) {
-        const uint4 a = *reinterpret_cast<const uint4 *>(row + 16 + 32 * blk), b = *reinterpret_cast<const uint4 *>(row + 32 + 32 * blk);
-        const uint32_t wv[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+// One 32-value block of a q8_0 row -> 16 registers of f16 pairs (register m = dims 2m, 2m+1 of the block), each value the
+// rounded product of the stored integer and the block's f16 scale, given as the pair d2.  d2 = 0 gives zeros whatever the
+// bytes are: the integer part is finite for every bit pattern.
+__device__ __forceinline__ void tc_block(const unsigned char * row, int blk, uint32_t d2, uint32_t (&r)[16]) {
+    const uint4 a = *reinterpret_cast<const uint4 *>(row + 16 + 32 * blk), b = *reinterpret_cast<const uint4 *>(row + 32 + 32 * blk);
+    const uint32_t wv[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const uint32_t x = wv[j] ^ 0x80808080u;
-            r[2 * j] = hmul2_u32(cvt_i8x2<0>(x), d2);
-            r[2 * j + 1] = hmul2_u32(cvt_i8x2<1>(x), d2);
-        }
-    } else {
-        // block at byte 18 blk: f16 scale, then 16 bytes (byte j = dim j | dim j + 16 << 4); 4-byte aligned for even blk
-        uint32_t q[4], sc;
-        if ((blk & 1) == 0) {
-            const uint32_t * p = reinterpret_cast<const uint32_t *>(row + 18 * blk);
-            const uint32_t w0 = p[0], w1 = p[1], w2 = p[2], w3 = p[3], w4 = p[4];
-            sc = w0;
-            q[0] = __funnelshift_r(w0, w1, 16); q[1] = __funnelshift_r(w1, w2, 16);
-            q[2] = __funnelshift_r(w2, w3, 16); q[3] = __funnelshift_r(w3, w4, 16);
-        } else {
-            const uint32_t * p = reinterpret_cast<const uint32_t *>(row + 18 * blk - 2);
-            sc = p[0] >> 16;
-            q[0] = p[1]; q[1] = p[2]; q[2] = p[3]; q[3] = p[4];
-        }
-        if (!live) sc = 0u;
-        const uint32_t dq = __byte_perm(sc, sc, 0x1010);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const uint32_t lo = q[j] & 0x0f0f0f0fu, hi = (q[j] >> 4) & 0x0f0f0f0fu;
-            r[2 * j] = hmul2_u32(cvt_n4x2<0>(lo), dq);
-            r[2 * j + 1] = hmul2_u32(cvt_n4x2<1>(lo), dq);
-            r[8 + 2 * j] = hmul2_u32(cvt_n4x2<0>(hi), dq);
-            r[8 + 2 * j + 1] = hmul2_u32(cvt_n4x2<1>(hi), dq);
-        }
+    for (int j = 0; j < 8; ++j) {
+        const uint32_t x = wv[j] ^ 0x80808080u;
+        r[2 * j] = hmul2_u32(cvt_i8x2<0>(x), d2);
+        r[2 * j + 1] = hmul2_u32(cvt_i8x2<1>(x), d2);
     }
 }
 
 // NC = score columns (16 for up to two verify rows, 32 for up to four): column 8 j + h = verify row j, head h of the group
 // (h < 6); columns with h = 6, 7 are padding (zero query rows).
-template <uint32_t KT, int NC>
+template <int NC>
 __global__ void __launch_bounds__(TC_THR, 1)
 decode_tc_k(const dec_args a, const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV) {
     extern __shared__ __align__(1024) unsigned char smem[];
-    constexpr int HB = traits<KT>::HB, BUF = UT * HB;
+    constexpr int HB = TC_HB, BUF = UT * HB;
     const int tid = threadIdx.x, lane = tid & 31;
     const int w = __shfl_sync(0xffffffffu, tid >> 5, 0);   // the warp index as a warp-uniform value
     const bool worker = w < TC_WORKERS / 32;
@@ -121,7 +93,7 @@ decode_tc_k(const dec_args a, const __grid_constant__ CUtensorMap mapK, const __
                                                                                  // workers run up to a tile ahead of the issuer)
     uint64_t * p_ready = full + 8;                                               // [2] P and the V image of a tile are written
     uint64_t * pv_done = full + 10;
-    uint32_t * tbase_p = reinterpret_cast<uint32_t *>(smem + 96);
+    uint32_t * tbase_p = reinterpret_cast<uint32_t *>(smem + 120);
     float * mref = reinterpret_cast<float *>(smem + 128);                        // [32] reference maximum per column (log2 units)
     float * fsc = reinterpret_cast<float *>(smem + 256);                         // [32] rescale factor of the last move
     float * wx = reinterpret_cast<float *>(smem + 384);                          // [4][32] per lane quarter: maxima / sums
@@ -206,10 +178,7 @@ decode_tc_k(const dec_args a, const __grid_constant__ CUtensorMap mapK, const __
                 const uint32_t q_s = smem_u32(QI), p_s = smem_u32(PI), v_s = smem_u32(VF);
                 auto qk = [&](int j) {   // tile j: waits for its K in tensor memory, queues Q K^T
                     const int G = g_u + j, b = G & 1;
-                    TC_T(q0);
                     tc_wait(&kconv[b], (uint32_t) ((G >> 1) & 1), a.status, 0);
-                    TC_T(q1);
-                    TC_ACC(8, q0, q1);
                     umma::fence_after_sync();
                     if (lead) {
 #pragma unroll
@@ -217,17 +186,12 @@ decode_tc_k(const dec_args a, const __grid_constant__ CUtensorMap mapK, const __
                             umma::mma_ts(tS_u + 32 * b, tA_u + 128 * b + ks * 8, umma::smem_desc(q_s + ks * 2 * (NC * 16), NC * 16, 128), id_qk, ks > 0);
                         umma::commit(&s_full[b]);
                     }
-                    TC_T(q2);
-                    TC_ACC(12, q1, q2);
                 };
                 qk(0);
                 for (int i = 0; i < nt_u; ++i) {
                     if (i + 1 < nt_u) qk(i + 1);
                     const int G = g_u + i;
-                    TC_T(p0);
                     tc_wait(&p_ready[G & 1], (uint32_t) ((G >> 1) & 1), a.status, 1);     // P and the V image are in place
-                    TC_T(p1);
-                    TC_ACC(10, p0, p1);
                     umma::fence_after_sync();
                     if (lead) {
 #pragma unroll
@@ -238,8 +202,6 @@ decode_tc_k(const dec_args a, const __grid_constant__ CUtensorMap mapK, const __
                                              umma::smem_desc(p_s + ks * 2 * TC_PLBO, TC_PLBO, 128), id_pv, (i > 0 || ks > 0) ? 1u : 0u);
                         umma::commit(pv_done);
                     }
-                    TC_T(p2);
-                    TC_ACC(13, p1, p2);
                 }
             } else {
                 const int klo_u = __shfl_sync(0xffffffffu, k_lo, 0), khi_u = __shfl_sync(0xffffffffu, k_hi, 0);
@@ -251,12 +213,8 @@ decode_tc_k(const dec_args a, const __grid_constant__ CUtensorMap mapK, const __
                         const int pq = q - TC_NBUF;
                         const bool was_v = pq > 0 && (pq & 1) == 0;
                         const int G = g_u + (pq == 0 ? 0 : was_v ? (pq - 2) >> 1 : (pq + 1) >> 1);
-                        TC_T(w0);
                         tc_wait(was_v ? &p_ready[G & 1] : &kconv[G & 1], (uint32_t) ((G >> 1) & 1), a.status, 7);
-                        TC_T(w1);
-                        TC_ACC(9, w0, w1);
                     }
-                    TC_T(i0);
                     const bool is_v = q == 2 * nt_u - 1 || (q > 0 && (q & 1) == 0);
                     const int tile = q == 0 ? 0 : q == 2 * nt_u - 1 ? nt_u - 1 : is_v ? (q - 2) >> 1 : (q + 1) >> 1;
                     const int p_t = klo_u + tile * UT;
@@ -276,8 +234,6 @@ decode_tc_k(const dec_args a, const __grid_constant__ CUtensorMap mapK, const __
                         }
                         if (lead) tma_box3(dst + h * TILE * HB, map, hk * (HB / 2), y, z, &full[buf]);
                     }
-                    TC_T(i1);
-                    TC_ACC(11, i0, i1);
                 }
             }
             __syncwarp();
@@ -300,22 +256,16 @@ decode_tc_k(const dec_args a, const __grid_constant__ CUtensorMap mapK, const __
             // The stores are left in flight: k_publish waits for them and tells the issuers.
             auto k_store = [&](int G) {
                 const int buf = cons & (TC_NBUF - 1);
-                TC_T(k0);
                 tc_wait(&full[buf], (uint32_t) ((cons >> 2) & 1), a.status, 2);
-                TC_T(k1);
-                TC_ACC(0, k0, k1);
                 ++cons;
                 const unsigned char * row = krow0 + buf * BUF;
-                uint32_t sc2 = 0;
-                if constexpr (KT == B200_KV_Q8_0) sc2 = *reinterpret_cast<const uint32_t *>(row + 4 * gq);   // the two blocks' scales
+                const uint32_t sc2 = *reinterpret_cast<const uint32_t *>(row + 4 * gq);   // the two blocks' scales
 #pragma unroll
                 for (int bb = 0; bb < 2; ++bb) {
                     uint32_t r[16];
-                    tc_block<KT>(row, 2 * gq + bb, __byte_perm(sc2, sc2, bb ? 0x3232 : 0x1010), true, r);
+                    tc_block(row, 2 * gq + bb, __byte_perm(sc2, sc2, bb ? 0x3232 : 0x1010), r);
                     umma::tmem_st16(tA + 128 * (G & 1) + lane_off + (2 * gq + bb) * 16, r);
                 }
-                TC_T(k2);
-                TC_ACC(1, k1, k2);
             };
             auto k_publish = [&](int G) {
                 umma::tmem_st_wait();
@@ -328,47 +278,30 @@ decode_tc_k(const dec_args a, const __grid_constant__ CUtensorMap mapK, const __
             k_publish(g);
             for (int i = 0; i < nt; ++i) {
                 const int G = g + i, p_t = k_lo + i * UT;
-#ifdef TC_PROF
-                long long t_mark = 0;
-#endif
                 if (i + 1 < nt) k_store(G + 1);
                 // ---- this tile's scores: the load from tensor memory flies during the V phase
-                TC_T(s0_);
                 tc_wait(&s_full[G & 1], (uint32_t) ((G >> 1) & 1), a.status, 5);
-                TC_T(s1_);
-                TC_ACC(5, s0_, s1_);
                 umma::fence_after_sync();
                 uint32_t sr[8];
                 if (act) umma::tmem_ld8(tS + 32 * (G & 1) + lane_off + 8 * gq, sr);
                 // ---- V rows -> f16 image, MN-major: byte(key, d) = (d / 8) * 128 + (key / 8) * 4096 + (key % 8) * 16 + (d % 8) * 2
                 {
                     const int buf = cons & (TC_NBUF - 1);
-                    TC_T(v0);
                     tc_wait(&full[buf], (uint32_t) ((cons >> 2) & 1), a.status, 3);
-                    TC_T(v1);
                     if (G > 0) tc_wait(pv_done, (uint32_t) ((G - 1) & 1), a.status, 4);   // the previous P V has read the image and P
-                    TC_T(v2);
-                    TC_ACC(2, v0, v1);
-                    TC_ACC(3, v1, v2);
-                    TC_MARK(t_mark);
                     ++cons;
                     const unsigned char * row = vrow0 + buf * BUF;
                     const bool valid = p_t + vkey < k_hi;   // rows past the run's last key may hold anything: they enter as zeros
 #pragma unroll
                     for (int u = 0; u < 2; ++u) {
-                        uint32_t r[16], d2 = 0;
-                        if constexpr (KT == B200_KV_Q8_0) {
-                            const uint32_t sc = valid ? *reinterpret_cast<const uint16_t *>(row + 2 * (vb + 4 * u)) : 0u;
-                            d2 = __byte_perm(sc, sc, 0x1010);
-                        }
-                        tc_block<KT>(row, vb + 4 * u, d2, valid, r);
+                        uint32_t r[16];
+                        const uint32_t sc = valid ? *reinterpret_cast<const uint16_t *>(row + 2 * (vb + 4 * u)) : 0u;
+                        tc_block(row, vb + 4 * u, __byte_perm(sc, sc, 0x1010), r);
 #pragma unroll
                         for (int c = 0; c < 4; ++c)
                             *reinterpret_cast<uint4 *>(vdst + u * 2048 + c * 128) = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
                     }
                 }
-                TC_T(s2_);
-                TC_ACC(4, t_mark, s2_);
                 if (i + 1 < nt) k_publish(G + 1);
                 // ---- scores of this thread's key for the six heads of verify row gq
                 float s[GQA], ofs[GQA];
@@ -457,8 +390,6 @@ decode_tc_k(const dec_args a, const __grid_constant__ CUtensorMap mapK, const __
                 umma::fence_before_sync();
                 __syncwarp();
                 if (lane == 0) tc_arrive(&p_ready[G & 1]);
-                TC_T(s3_);
-                TC_ACC(6, s2_, s3_);
             }
             // ---------------- the run's partial (O, reference maximum, sum) ----------------
             tc_wait(pv_done, (uint32_t) ((g + nt - 1) & 1), a.status, 6);

@@ -267,11 +267,12 @@ def test_verify_batch_vs_oracle(cuda, lib, tname, chunk):
     util.check_close(got, ref, "verify batch %s chunk=%d" % (tname, chunk))
 
 
-@pytest.mark.parametrize("tname", ["q8_0", "q4_0"])
-@pytest.mark.parametrize("q_len", [1, 2, 3, 4])
+@pytest.mark.parametrize("tname", ["q8_0"])
+@pytest.mark.parametrize("q_len", [2, 3, 4])
 def test_even_split_kernels_agree(cuda, lib, tname, q_len):
-    """the even split runs quantised caches on the tcgen05 kernel; the mma.sync kernel (set_tc(0)) must give the same
-    result within the tolerance, and both must match the oracle, for every row count and ragged contexts"""
+    """the even split runs q8_0 verify batches (two to four rows per slot) on the tcgen05 kernel; the mma.sync kernel
+    (set_tc(0)) must give the same result within the tolerance, and both must match the oracle, for every row count and
+    ragged contexts"""
     lens = [5000, 130, 64, 4, 2049, 767, 128, 1]
     lens = [max(n, q_len) for n in lens]
     assert lib.b200_attn_dec_tc() == 1
