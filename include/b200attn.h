@@ -121,7 +121,7 @@ int b200_rope_append_bf16_at(const uint16_t *q, const uint16_t *k, const uint16_
 /* attn_decode (attn.cuh:44, attn.cu:638): q, out [T][Hq][D] f32, row t at position p0+t sees keys 0..p0+t. T <= 8. */
 int b200_attn_decode(const float *q, const b200_kv_cache *c, float *out, int T, int p0, int Hq, float scale, void *stream);
 /* attn_decode_dev (attn.cuh:59, attn.cu:654): p0 read from *p0_dev on the device; grid sized for p0+T <= max_n
- * (max_n <= 0: the cache's n_ctx).  A position beyond max_n is reported through the status word (bit 8) and the keys
+ * (max_n <= 0: the cache's n_ctx).  A position beyond max_n is reported through the status word (value 8) and the keys
  * past the limit are left out; nothing is read out of bounds. */
 int b200_attn_decode_dev(const float *q, const b200_kv_cache *c, float *out, int T, const int32_t *p0_dev, int max_n,
                          int Hq, float scale, void *stream);
@@ -337,7 +337,9 @@ int b200_session_read_rank(int fd, b200_pool *p, int slot, int pages, void *stat
 /* ---------------------------------------------------------------- diagnostics -------------------------------- */
 /* Kernels never trap or spin without a limit: a wait that runs out, or an address check that fails, records a code
  * in a device status word and the kernel returns.  This reads (and clears) that word for the current device after
- * synchronising the given stream; 0 = no error. */
+ * synchronising the given stream; 0 = no error.  Codes (or-ed): 1 a bounded wait gave up, 2 a negative page-table entry,
+ * 4 a misaligned address, 8 a row position beyond max_n / n_ctx; 0x100 << k names the wait of the tcgen05 verify kernel
+ * that gave up (k = 0 K operand, 1 P, 2 K rows, 3 V rows, 4 previous P V, 5 scores, 6 last P V, 7 a free staging buffer). */
 int b200_last_device_status(void *stream);
 /* launches of this library's kernels since load (all devices), for benchmark bookkeeping */
 uint64_t b200_launch_count(void);

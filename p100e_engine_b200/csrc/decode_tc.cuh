@@ -215,23 +215,32 @@ decode_tc_k(const dec_args a, const __grid_constant__ CUtensorMap mapK, const __
                         const int G = g_u + (pq == 0 ? 0 : was_v ? (pq - 2) >> 1 : (pq + 1) >> 1);
                         tc_wait(was_v ? &p_ready[G & 1] : &kconv[G & 1], (uint32_t) ((G >> 1) & 1), a.status, 7);
                     }
-                    const bool is_v = q == 2 * nt_u - 1 || (q > 0 && (q & 1) == 0);
-                    const int tile = q == 0 ? 0 : q == 2 * nt_u - 1 ? nt_u - 1 : is_v ? (q - 2) >> 1 : (q + 1) >> 1;
-                    const int p_t = klo_u + tile * UT;
-                    const int buf = (ib_u + q) & (TC_NBUF - 1);
-                    unsigned char * dst = stg + (size_t) buf * BUF;
-                    const CUtensorMap * map = is_v ? &mapV : &mapK;
-                    const int nbox = p_t + TILE < khi_u ? 2 : 1;   // 64-position boxes that hold keys of the run
-                    if (lead) mbar_expect_tx(&full[buf], (uint32_t) nbox * TILE * HB);
-                    for (int h = 0; h < nbox; ++h) {
-                        const int p = p_t + h * TILE;
-                        int y = p, z = 0;
+                    // the item's 64-position boxes: (tensor map, row in page, page) of box h; boxes past the run's end hold no key
+                    auto boxes = [&](int item, const CUtensorMap *& map, int & p_t) {
+                        const bool is_v = item == 2 * nt_u - 1 || (item > 0 && (item & 1) == 0);
+                        const int tile = item == 0 ? 0 : item == 2 * nt_u - 1 ? nt_u - 1 : is_v ? (item - 2) >> 1 : (item + 1) >> 1;
+                        p_t = klo_u + tile * UT;
+                        map = is_v ? &mapV : &mapK;
+                        return p_t + TILE < khi_u ? 2 : 1;
+                    };
+                    auto coords = [&](int p, int & y, int & z) {
+                        y = p; z = 0;
                         if (tab) {
                             const int idx = (p >> a.g.psh) - pg0_u;
                             z = idx < TC_PGS ? pgs[idx] : tab[p >> a.g.psh];
                             y = p & ((1 << a.g.psh) - 1);
                             if (z < 0) { if (lead) atomicOr(a.status, ST_BAD_PAGE); z = 0; }
                         }
+                    };
+                    const CUtensorMap * map;
+                    int p_t;
+                    const int nbox = boxes(q, map, p_t);
+                    const int buf = (ib_u + q) & (TC_NBUF - 1);
+                    unsigned char * dst = stg + (size_t) buf * BUF;
+                    if (lead) mbar_expect_tx(&full[buf], (uint32_t) nbox * TILE * HB);
+                    for (int h = 0; h < nbox; ++h) {
+                        int y, z;
+                        coords(p_t + h * TILE, y, z);
                         if (lead) tma_box3(dst + h * TILE * HB, map, hk * (HB / 2), y, z, &full[buf]);
                     }
                 }

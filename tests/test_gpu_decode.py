@@ -223,20 +223,21 @@ def test_small_pages_take_the_row_copies(cuda, lib, tname):
     assert fast.device_status() == 0
 
 
-def _verify_batch(cuda, kt, n_slots, q_len, lens, seed, chunk_keys, gate_on=True):
+def _verify_batch(cuda, kt, n_slots, q_len, lens, seed, chunk_keys, gate_on=True, psh=8):
     """config-2 style batch: slots with their own contexts in a shared pool; returns (got, oracle)"""
     import torch
     from p100e_engine_b200 import fast
-    maxp = (max(lens) + 255) // 256
-    total = sum((n + 255) // 256 for n in lens)
-    pool = util.PagedPool(kt, total + 3, psh=8, seed=seed)
+    pg = 1 << psh
+    maxp = (max(lens) + pg - 1) // pg
+    total = sum((n + pg - 1) // pg for n in lens)
+    pool = util.PagedPool(kt, total + 3, psh=psh, seed=seed)
     pts = np.stack([pool.take(n, maxp) for n in lens])
     pool_t = torch.zeros(pool.bytes, dtype=torch.uint8, device=cuda)
     pt_t = util.to_dev(pts.reshape(-1), cuda)
     for s, n in enumerate(lens):
         k = util.to_dev(util.rng_normal(seed * 100 + 2 * s, (n, HKV, D)), cuda)
         v = util.to_dev(util.rng_normal(seed * 100 + 2 * s + 1, (n, HKV, D)), cuda)
-        pc = util.dev_cache(pool_t, pool, pt_t[s * maxp:(s + 1) * maxp], None, maxp << 8)
+        pc = util.dev_cache(pool_t, pool, pt_t[s * maxp:(s + 1) * maxp], None, maxp << psh)
         for p in range(0, n, 8192):
             T = min(8192, n - p)
             assert fast.kv_append(pc, k[p:p + T], v[p:p + T], p, T)
@@ -247,13 +248,13 @@ def _verify_batch(cuda, kt, n_slots, q_len, lens, seed, chunk_keys, gate_on=True
     rtab = np.array([s * maxp for s in range(n_slots) for _ in range(q_len)], np.int32)
     q = util.rng_normal(seed + 1, (rows, HQ, D))
     gate = util.rng_normal(seed + 2, (rows, HQ * D)) if gate_on else None
-    c = util.dev_cache(pool_t, pool, pt_t, util.to_dev(rtab, cuda), maxp << 8)
+    c = util.dev_cache(pool_t, pool, pt_t, util.to_dev(rtab, cuda), maxp << psh)
     out = torch.zeros(rows, HQ, D, device=cuda)
     assert fast.attn_decode_slots(util.to_dev(q, cuda), c, out, None if gate is None else util.to_dev(gate, cuda), n_slots,
                                   q_len, util.to_dev(pos, cuda), max(lens), HQ, SCALE, chunk_keys)
     torch.cuda.synchronize()
     assert fast.device_status() == 0
-    hc = pool.host_cache(pts.reshape(-1), rtab, maxp << 8)
+    hc = pool.host_cache(pts.reshape(-1), rtab, maxp << psh)
     ref = orc.attention(q, hc, rows, HQ, SCALE, pos=pos, gate=gate)
     return out.cpu().numpy(), ref, (q, gate, pos, rtab, c, pool, pool_t, pt_t)
 
@@ -286,6 +287,32 @@ def test_even_split_kernels_agree(cuda, lib, tname, q_len):
     util.check_close(got_tc, ref, "even split, tcgen05 kernel (%s, q_len %d)" % (tname, q_len))
     util.check_close(got_mma, ref, "even split, mma.sync kernel (%s, q_len %d)" % (tname, q_len))
     util.check_close(got_tc, got_mma, "tcgen05 vs mma.sync (%s, q_len %d)" % (tname, q_len))
+
+
+def test_even_split_64_row_pages_and_long_page_lists(cuda, lib):
+    """the tcgen05 kernel fetches 64-position boxes: pages of exactly 64 rows, a run with more pages than the kernel keeps
+    in shared memory (a 20,000-key slot = 313 pages), a slot that ends one key into a page"""
+    lens = [20000, 300, 65, 4097]
+    got, ref, _ = _verify_batch(cuda, TYPES["q8_0"], len(lens), 4, lens, 23, -1, psh=6)
+    util.check_close(got, ref, "even split, 64-row pages")
+
+
+def test_even_split_contiguous_cache_several_row_groups(cuda, lib):
+    """the batched entry point on a contiguous cache: three row groups at different depths of one sequence, chosen split"""
+    import torch
+    from p100e_engine_b200 import fast
+    n, q_len = 5000, 4
+    c, oc = _filled(TYPES["q8_0"], n, cuda, seed=91)
+    starts = [n - q_len, 1900, 130]
+    pos = np.array([s0 + j for s0 in starts for j in range(q_len)], np.int32)
+    rows = len(pos)
+    q = util.rng_normal(92, (rows, HQ, D))
+    out = torch.zeros(rows, HQ, D, device=cuda)
+    assert fast.attn_decode_slots(util.to_dev(q, cuda), c, out, None, len(starts), q_len, util.to_dev(pos, cuda), n, HQ, SCALE, -1)
+    torch.cuda.synchronize()
+    assert fast.device_status() == 0
+    ref = orc.attention(q, oc, rows, HQ, SCALE, pos=pos)
+    util.check_close(out.cpu().numpy(), ref, "even split, contiguous cache")
 
 
 def test_slot_rows_independent_of_batch(cuda, lib):
