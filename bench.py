@@ -56,6 +56,10 @@ WORKLOADS = {
 }
 
 
+def rank_of(plan):
+    return plan.rank
+
+
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -72,6 +76,9 @@ def parse():
     ap.add_argument("--breakdown", action="store_true", help="add per-layer times of the step's parts (an extra eager pass)")
     ap.add_argument("--q-len", type=int, default=0, help="override the workload's query rows per slot (1..4)")
     ap.add_argument("--seq-shards", type=int, default=0, help="force the number of sequence shards (default: only when N > 4)")
+    ap.add_argument("--sub-batches", type=int, default=1, help="with sequence shards: the slots go in this many groups on as many streams")
+    ap.add_argument("--exchange", default="peers", choices=["peers", "nccl"],
+                    help="with sequence shards: partials read in place over peer-mapped buffers (one kernel), or ncclAllGather + merge")
     ap.add_argument("--seed", type=int, default=0xB200)
     return ap.parse_args()
 
@@ -355,8 +362,10 @@ class Workload:
         self.gate = torch.empty(self.rows, hq * D, device=dev)
         self.out = torch.empty(self.rows, hq, D, device=dev)
         self.chunk = args.chunk
-        # sequence shards: the slots go in two halves on two streams, so the exchange of one half runs beside the attention
-        # of the other (inside a layer; layers stay in order)
+        # sequence shards: the shards' partials are merged in place over peer-mapped buffers (one kernel per layer; NCCL
+        # all-gather + merge if the mapping is not available or --exchange nccl).  --sub-batches n > 1 puts the slots in n
+        # groups on n streams, so that the exchange of one group runs beside the attention of another (inside a layer;
+        # layers stay in order)
         self.merge = None
         self.in_group = None
         if plan.n_seq > 1:
@@ -364,14 +373,25 @@ class Workload:
             import torch.distributed as dist
             groups = [dist.new_group(r) for r in plan.all_merge_groups()]
             group, ranks = groups[plan.head_rank], plan.merge_group_ranks()
-            self.nsub = 2 if slots >= 2 else 1
+            self.nsub = max(1, min(args.sub_batches, slots))
             cut = [slots * i // self.nsub for i in range(self.nsub + 1)]
             self.sub = [(cut[i], cut[i + 1]) for i in range(self.nsub)]
             # one raw NCCL communicator per stream that exchanges (the two sub-batch streams, the upload stream): the
             # collectives are enqueued on those streams themselves
-            self.comms = [Dm.NcclComm(ranks, group, dev) for _ in range(self.nsub + 1)]
-            self.in_comm = self.comms[self.nsub]
-            self.merge = [Dm.SeqMerge(plan, (b - a) * q_len, hq, D, dev, group, self.comms[i]) for i, (a, b) in enumerate(self.sub)]
+            self.peers = args.exchange == "peers"
+            self.comms = [Dm.NcclComm(ranks, group, dev) for _ in range((0 if self.peers else self.nsub) + 1)]
+            self.in_comm = self.comms[-1]
+            self.group = group
+            if self.peers:
+                try:
+                    self.merge = [Dm.PeerMerge(plan, (b - a) * q_len, hq, D, dev, group) for a, b in self.sub]
+                except RuntimeError as e:   # raised on every shard of the group alike
+                    if rank_of(plan) == 0:
+                        sys.stderr.write("bench.py: %s; exchanging through NCCL instead\n" % e)
+                    self.peers = False
+                    self.comms = [Dm.NcclComm(ranks, group, dev) for _ in range(self.nsub)] + self.comms
+            if not self.peers:
+                self.merge = [Dm.SeqMerge(plan, (b - a) * q_len, hq, D, dev, group, self.comms[i]) for i, (a, b) in enumerate(self.sub)]
             self.sub_streams = [torch.cuda.Stream() for _ in range(self.nsub)]
             self.ev_prep = torch.cuda.Event()
             self.ev_sub = [torch.cuda.Event() for _ in range(self.nsub)]
@@ -520,9 +540,14 @@ class Workload:
         if self.merge is not None:
             import torch.distributed as dist
             from p100e_engine_b200 import dist as Dm
-            names += ["copy into place + all-gather of (O, m, l) in the pair (NCCL)", "merge of the shards + gate"]
-            if not hasattr(self, "bd_merge"):
-                self.bd_merge = Dm.SeqMerge(self.plan, self.rows, self.hq, D, self.dev, self.merge[0].group, self.comms[0])
+            if self.peers:
+                names += ["merge of the shards over peer-mapped partials + gate (one kernel, includes the wait for the peer)"]
+                if not hasattr(self, "bd_merge"):
+                    self.bd_merge = Dm.PeerMerge(self.plan, self.rows, self.hq, D, self.dev, self.group)
+            else:
+                names += ["copy into place + all-gather of (O, m, l) in the pair (NCCL)", "merge of the shards + gate"]
+                if not hasattr(self, "bd_merge"):
+                    self.bd_merge = Dm.SeqMerge(self.plan, self.rows, self.hq, D, self.dev, self.group, self.comms[0])
             mg = self.bd_merge
         acc = np.zeros(len(names))
         host = 0.0
@@ -545,11 +570,15 @@ class Workload:
                     ok = ok and fast.attn_decode_slots_partial(self.q, c, po, pm, pl, self.slots, self.q_len, self.last_key, self.max_n,
                                                                self.hq, SCALE, self.chunk)
                     ev[l][2].record()
-                    mg.recv[self.plan.seq_rank].copy_(mg.send)
-                    mg.comm.all_gather_f32(mg.recv)
-                    ev[l][3].record()
-                    ok = ok and fast.seq_exchange_merge(0, self.plan.n_seq, mg.send, mg.recv, mg.R, D, self.gate, self.out.view(mg.R, D))
-                    ev[l][4].record()
+                    if self.peers:
+                        mg.exchange_and_merge(self.gate, self.out.view(mg.R, D))
+                        ev[l][3].record()
+                    else:
+                        mg.recv[self.plan.seq_rank].copy_(mg.send)
+                        mg.comm.all_gather_f32(mg.recv)
+                        ev[l][3].record()
+                        ok = ok and fast.seq_exchange_merge(0, self.plan.n_seq, mg.send, mg.recv, mg.R, D, self.gate, self.out.view(mg.R, D))
+                        ev[l][4].record()
                 assert ok
             t1 = time.perf_counter()
             torch.cuda.synchronize()
@@ -677,6 +706,9 @@ def run_b200(args):
     kname = "decode_tc_k" if tc else "decode_part_k"
     tr = traffic_ratios().get(kname, {})
     line = base_line(args, wl.slots, wl.q_len, wl.layers)
+    if plan.n_seq > 1:
+        line["config"]["exchange"] = ("partials merged in place over peer-mapped buffers" if wl.peers else "ncclAllGather of the partials + merge") + \
+            ", %d sub-batch(es)" % wl.nsub
     line["config"].update({"parallelism": "kv-head shards %d x sequence shards %d" % (plan.n_head_shards, plan.n_seq),
                            "keys_per_layer": int(wl.n_ctx.sum()), "chunk_keys": args.chunk,
                            "l2": "inputs larger than L2 (%.1f GB of KV per step per GPU)" % (wl.kv_bytes_layer * wl.layers / 1e9),

@@ -225,6 +225,25 @@ int b200_seq_exchange_merge(void *nccl_comm, int n_seq, const float *send, float
 int b200_seq_exchange_merge_a16(void *nccl_comm, int n_seq, const float *send, float *recv, int R, int D,
                                 const float *gate, float *out, void *qbuf, void *stream);
 
+/* The same step without a collective: every shard keeps its partial in a buffer that the other shards of its group have
+ * mapped (one process per GPU on one node: b200_peer_alloc gives the buffer and a 64-byte handle, b200_peer_open maps a
+ * peer's handle; cudaMalloc / cudaIpcGetMemHandle / cudaIpcOpenMemHandle underneath).  parts[s], flags[s] (host arrays of
+ * n_seq <= 8 device addresses, in shard order): shard s's partial [O (R*D) | m (R) | l (R)] and its row of n_seq flag
+ * words, as seen from this process (own buffer for s == me).  One kernel announces "my partial of call `epoch` is complete"
+ * in every peer's flag row, waits (bounded: 2 s, then the status word gets code 1) for the peers' announcements, and merges
+ * in shard order reading the peers' rows over NVLink.  epoch = 1, 2, 3, .. in step on all shards of the group; the caller
+ * alternates two partial buffers by the parity of the epoch (a shard rewrites a buffer two calls after it was merged, when
+ * every peer has moved past it), and the flag rows start zeroed.  Results equal b200_seq_exchange_merge bit for bit. */
+int b200_peer_alloc(size_t bytes, void **ptr, unsigned char *handle64);
+int b200_peer_open(const unsigned char *handle64, void **ptr);
+int b200_peer_close(void *ptr);
+int b200_peer_free(void *ptr);
+int b200_seq_merge_peers(const void *const *parts, void *const *flags, int n_seq, int me, unsigned epoch, int R, int D,
+                         const float *gate, float *out, void *stream);
+int b200_seq_merge_peers_a16(const void *const *parts, void *const *flags, int n_seq, int me, unsigned epoch, int R, int D,
+                             const float *gate, float *out, void *qbuf, void *stream);
+
+
 /* ---------------------------------------------------------------- prefill ------------------------------------ */
 /* attn_prefill / attn_prefill_variant (attn.cuh:46-53, attn.cu:457-499): any T >= 1, query t at p0+t sees 0..p0+t;
  * the cache must already hold 0..p0+T-1.  Uses library scratch: one buffer per (device, stream), allocated on first use,

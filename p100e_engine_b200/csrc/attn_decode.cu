@@ -858,6 +858,82 @@ __global__ void merge_parts_k(const float * __restrict__ po, const float * __res
     if (qbuf) a16_store_lanes8(y, qbuf, ((size_t) r * D + 4 * i) / 32, (size_t) R * D / 32, true);
 }
 
+// The same merge with the shards' partials read in place: shard s of a sequence split keeps its partial [O (R*D) | m (R) | l (R)]
+// in a buffer that its peers have mapped (part[s]: this GPU's own buffer for s == me, a peer mapping otherwise) and a row of
+// flag words flag[s][0..n_seq) that shard j writes at index j.  A call with epoch e (1, 2, .. in step on all shards)
+//   1. tells every peer "my partial of call e is complete" (the kernel that wrote it ran before this one on the stream),
+//   2. waits, bounded, until every peer has said the same,
+//   3. merges in shard order, reading the peers' rows over NVLink with plain loads that bypass L1.
+// The caller alternates two partial buffers by the parity of e: a peer that announces call e + 1 has finished reading the
+// buffer of call e, and this shard passes step 2 of call e + 1 before the kernel that rewrites that buffer (call e + 2)
+// can start.  One block per row, D/4 threads; the first four blocks announce, every block waits by itself.
+constexpr int MAX_PEERS = 8;
+struct peer_parts { const float * part[MAX_PEERS]; unsigned * flag[MAX_PEERS]; };
+
+__device__ __forceinline__ float4 ld_sys_f4(const float * p) {
+    float4 v;
+    asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ float ld_sys_f(const float * p) {
+    float v;
+    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__global__ void merge_peers_k(const peer_parts pp, int n_seq, int me, unsigned epoch, int R, int D, const float * __restrict__ gate,
+                              float * __restrict__ out, __half2 * __restrict__ qbuf, unsigned * __restrict__ status) {
+    const int r = blockIdx.x, i = threadIdx.x;
+    // the first blocks of the grid announce (any one would do; a few, so that the announcement does not hang on one block's
+    // turn); every block waits by itself
+    if (r < 4 && i < n_seq && i != me)
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pp.flag[i] + me), "r"(epoch) : "memory");
+    if (i < n_seq && i != me) {
+        const unsigned * f = pp.flag[me] + i;
+        unsigned v;
+        const unsigned long long t0 = globaltimer_ns();
+        for (int it = 0;; ++it) {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+            if ((int) (v - epoch) >= 0) break;
+            if ((it & 63) == 63 && globaltimer_ns() - t0 > 2000000000ull) { atomicOr(status, ST_WAIT_TIMEOUT); break; }
+        }
+    }
+    __syncthreads();
+    const size_t om = (size_t) R * D, ol = om + R;
+    float ms[MAX_PEERS];
+    float M = B200_NEG_INF;
+#pragma unroll
+    for (int s = 0; s < MAX_PEERS; ++s) {
+        ms[s] = B200_NEG_INF;
+        if (s < n_seq) ms[s] = s == me ? pp.part[s][om + r] : ld_sys_f(pp.part[s] + om + r);
+        M = fmaxf(M, ms[s]);
+    }
+    float den = 0.0f;
+    float4 num = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+    for (int s = 0; s < MAX_PEERS; ++s) {
+        if (s >= n_seq || ms[s] == B200_NEG_INF) continue;
+        const float f = ex2f((ms[s] - M) * LOG2E);
+        const float * po = pp.part[s] + (size_t) r * D + 4 * i;
+        const float l = s == me ? pp.part[s][ol + r] : ld_sys_f(pp.part[s] + ol + r);
+        const float4 o = s == me ? *reinterpret_cast<const float4 *>(po) : ld_sys_f4(po);
+        den = fmaf(f, l, den);
+        num.x = fmaf(f, o.x, num.x); num.y = fmaf(f, o.y, num.y); num.z = fmaf(f, o.z, num.z); num.w = fmaf(f, o.w, num.w);
+    }
+    float4 y = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (den > 0.0f) {
+        const float inv = 1.0f / den;
+        y = make_float4(num.x * inv, num.y * inv, num.z * inv, num.w * inv);
+        if (gate) {
+            const float4 gv = reinterpret_cast<const float4 *>(gate + (size_t) r * D)[i];
+            y.x *= 1.0f / (1.0f + expf(-gv.x)); y.y *= 1.0f / (1.0f + expf(-gv.y));
+            y.z *= 1.0f / (1.0f + expf(-gv.z)); y.w *= 1.0f / (1.0f + expf(-gv.w));
+        }
+    }
+    reinterpret_cast<float4 *>(out + (size_t) r * D)[i] = y;
+    if (qbuf) a16_store_lanes8(y, qbuf, ((size_t) r * D + 4 * i) / 32, (size_t) R * D / 32, true);
+}
+
 // Work list of a batched call: every (slot, chunk) that holds at least one visible key, longest first.  Whole chunks
 // come first (all the same length), then the slots' last, shorter chunks in descending order of their tile count, so the
 // tail of the launch is made of the shortest units.  One block; writes units[] and *n_units.  The order of equal-length
@@ -1592,6 +1668,66 @@ int b200_seq_exchange_merge_a16(void * nccl_comm, int n_seq, const float * send,
                                 float * out, void * qbuf, void * stream) {
     if (!qbuf) B200_REFUSE(B200_ERR_SHAPE, "seq_exchange_merge_a16: qbuf is null");
     return seq_exchange_impl(nccl_comm, n_seq, send, recv, R, D, gate, out, qbuf, stream, "seq_exchange_merge_a16");
+}
+
+// ---- sequence split over peer-mapped buffers ------------------------------------------------------------------
+// A buffer other processes of the node can map (cudaMalloc + cudaIpcGetMemHandle): the host passes the 64-byte handle to the
+// peers by whatever means it has, they map it with b200_peer_open.  Zero-filled.
+int b200_peer_alloc(size_t bytes, void ** ptr, unsigned char * handle) {
+    if (!ptr || !handle || !bytes) B200_REFUSE(B200_ERR_SHAPE, "peer_alloc: null argument");
+    void * p = nullptr;
+    if (cudaMalloc(&p, bytes) != cudaSuccess) { cudaGetLastError(); B200_REFUSE(B200_ERR_ALLOC, "peer_alloc: cudaMalloc(%zu) failed", bytes); }
+    cudaIpcMemHandle_t h;
+    if (cudaMemset(p, 0, bytes) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess || cudaIpcGetMemHandle(&h, p) != cudaSuccess) {
+        const cudaError_t e = cudaGetLastError();
+        cudaFree(p);
+        B200_REFUSE(B200_ERR_CUDA, "peer_alloc: %s", cudaGetErrorString(e));
+    }
+    static_assert(sizeof h == 64, "handle size");
+    memcpy(handle, &h, 64);
+    *ptr = p;
+    return B200_OK;
+}
+int b200_peer_open(const unsigned char * handle, void ** ptr) {
+    if (!ptr || !handle) B200_REFUSE(B200_ERR_SHAPE, "peer_open: null argument");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    void * p = nullptr;
+    const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) { cudaGetLastError(); B200_REFUSE(B200_ERR_CUDA, "peer_open: %s", cudaGetErrorString(e)); }
+    *ptr = p;
+    return B200_OK;
+}
+int b200_peer_close(void * ptr) { return ptr && cudaIpcCloseMemHandle(ptr) != cudaSuccess ? (cudaGetLastError(), B200_ERR_CUDA) : B200_OK; }
+int b200_peer_free(void * ptr) { return ptr && cudaFree(ptr) != cudaSuccess ? (cudaGetLastError(), B200_ERR_CUDA) : B200_OK; }
+
+static int seq_merge_peers_impl(const void * const * parts, void * const * flags, int n_seq, int me, unsigned epoch, int R, int D,
+                                const float * gate, float * out, void * qbuf, void * stream, const char * who) {
+    if (!parts || !flags || !out || n_seq < 1 || n_seq > MAX_PEERS || me < 0 || me >= n_seq || R < 1 || D % 4 || D < 4 * MAX_PEERS || D > 4096 ||
+        !aligned16(out) || (gate && !aligned16(gate)))
+        B200_REFUSE(B200_ERR_SHAPE, "%s: unsupported arguments", who);
+    if (qbuf && (D % 128 || ((uintptr_t) qbuf & 3))) B200_REFUSE(B200_ERR_SHAPE, "%s: the a16 buffer needs D %% 128 == 0 and 4-byte alignment", who);
+    peer_parts pp;
+    for (int s = 0; s < MAX_PEERS; ++s) {
+        pp.part[s] = s < n_seq ? (const float *) parts[s] : nullptr;
+        pp.flag[s] = s < n_seq ? (unsigned *) flags[s] : nullptr;
+        if (s < n_seq && (!pp.part[s] || !pp.flag[s] || !aligned16(pp.part[s]) || ((uintptr_t) pp.flag[s] & 3)))
+            B200_REFUSE(B200_ERR_SHAPE, "%s: shard %d: buffers must be mapped and 16-byte aligned", who, s);
+    }
+    unsigned * st = device_status_word();
+    if (!st) return B200_ERR_CUDA;
+    merge_peers_k<<<R, D / 4, 0, (cudaStream_t) stream>>>(pp, n_seq, me, epoch, R, D, gate, out, (__half2 *) qbuf, st);
+    count_launch();
+    return launch_status(who);
+}
+int b200_seq_merge_peers(const void * const * parts, void * const * flags, int n_seq, int me, unsigned epoch, int R, int D,
+                         const float * gate, float * out, void * stream) {
+    return seq_merge_peers_impl(parts, flags, n_seq, me, epoch, R, D, gate, out, nullptr, stream, "seq_merge_peers");
+}
+int b200_seq_merge_peers_a16(const void * const * parts, void * const * flags, int n_seq, int me, unsigned epoch, int R, int D,
+                             const float * gate, float * out, void * qbuf, void * stream) {
+    if (!qbuf) B200_REFUSE(B200_ERR_SHAPE, "seq_merge_peers_a16: qbuf is null");
+    return seq_merge_peers_impl(parts, flags, n_seq, me, epoch, R, D, gate, out, qbuf, stream, "seq_merge_peers_a16");
 }
 
 }  // extern "C"

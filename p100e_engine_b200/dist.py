@@ -156,6 +156,72 @@ class SeqMerge:
             raise RuntimeError("seq_exchange_merge refused")
 
 
+class PeerMerge:
+    """Merge of sequence-shard partials read in place over peer-mapped buffers (one process per GPU on one node): no
+    collective in the path.  Every shard owns two partial buffers (used alternately) and a row of flag words in one
+    buffer from b200_peer_alloc; the handles go round the group once, at construction.  Same interface as SeqMerge."""
+
+    def __init__(self, plan, rows, hq_local, d=256, device=None, group=None):
+        import torch
+        import torch.distributed as dist
+        from . import fast
+        self.plan, self.rows, self.hq, self.d = plan, rows, hq_local, d
+        R = rows * hq_local
+        self.R = R
+        self.part_bytes = (R * (d + 2) * 4 + 255) // 256 * 256
+        self.flag_off = 2 * self.part_bytes
+        n, me = plan.n_seq, plan.seq_rank
+        # every shard runs the same collectives whatever happens locally, and all of them learn whether all mappings exist
+        err = None
+        try:
+            self.own, handle = fast.peer_alloc(self.flag_off + 256)
+        except Exception as e:   # noqa: BLE001 - reported to the whole group below
+            self.own, handle, err = 0, b"", e
+        handles = [None] * n
+        dist.all_gather_object(handles, handle, group=group)
+        self.base = []
+        for s in range(n):
+            try:
+                self.base.append(self.own if s == me else fast.peer_open(handles[s]) if (err is None and handles[s]) else 0)
+            except Exception as e:   # noqa: BLE001
+                self.base.append(0)
+                err = err or e
+        ok = torch.tensor([0 if (err is not None or 0 in self.base) else 1], dtype=torch.int32, device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)   # also: every flag row is zeroed and mapped before the first call
+        if int(ok.item()) == 0:
+            self.close()
+            raise RuntimeError("peer-mapped buffers are not available in this group: %r" % (err,))
+        self.me, self.epoch, self.torch, self.device = me, 0, torch, device
+
+    def close(self):
+        from . import fast
+        for s, b in enumerate(getattr(self, "base", [])):
+            if b and b != self.own:
+                fast.peer_close(b)
+        if getattr(self, "own", 0):
+            fast.peer_free(self.own)
+        self.base, self.own = [], 0
+
+    def _views(self, parity):
+        """(part_o, part_m, part_l) device addresses of this shard's buffer of the given parity"""
+        R, d = self.R, self.d
+        b = self.own + parity * self.part_bytes
+        return b, b + R * d * 4, b + (R * d + R) * 4
+
+    def views(self):
+        """where the next call's partial goes (b200_attn_decode_slots_partial takes the addresses)"""
+        return self._views((self.epoch + 1) & 1)
+
+    def exchange_and_merge(self, gate, out, qbuf=None):
+        from . import fast
+        self.epoch += 1
+        par = self.epoch & 1
+        parts = [b + par * self.part_bytes for b in self.base]
+        flags = [b + self.flag_off for b in self.base]
+        if not fast.seq_merge_peers(parts, flags, self.me, self.epoch, self.R, self.d, gate, out, qbuf):
+            raise RuntimeError("seq_merge_peers refused")
+
+
 def merge_partials_host(parts_o, parts_m, parts_l):
     """numpy statement of the merge (for CPU tests of the exchange logic): parts_* [n][R][D] / [n][R] -> [R][D]"""
     parts_o = np.asarray(parts_o, np.float64)

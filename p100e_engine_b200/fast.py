@@ -129,6 +129,38 @@ def seq_exchange_merge_a16(nccl_comm, n_seq, send, recv, R, D, gate, out, qbuf, 
                                                 L.ptr(out), L.ptr(qbuf), _stream(s)) == L.OK
 
 
+def peer_alloc(nbytes):
+    """(device address, 64-byte handle) of a zero-filled buffer that other processes of the node can map"""
+    p, h = C.c_void_p(), (C.c_ubyte * 64)()
+    L.check("b200_peer_alloc", L.load().b200_peer_alloc(nbytes, C.byref(p), h))
+    return p.value, bytes(h)
+
+
+def peer_open(handle):
+    """device address of a peer's buffer in this process"""
+    p, h = C.c_void_p(), (C.c_ubyte * 64).from_buffer_copy(handle)
+    L.check("b200_peer_open", L.load().b200_peer_open(h, C.byref(p)))
+    return p.value
+
+
+def peer_close(ptr):
+    return L.load().b200_peer_close(C.c_void_p(ptr)) == L.OK
+
+
+def peer_free(ptr):
+    return L.load().b200_peer_free(C.c_void_p(ptr)) == L.OK
+
+
+def seq_merge_peers(parts, flags, me, epoch, R, D, gate, out, qbuf=None, s=None):
+    """merge of the shards' partials read in place over peer mappings; parts / flags: device addresses in shard order"""
+    n = len(parts)
+    pa, fa = (C.c_void_p * n)(*parts), (C.c_void_p * n)(*flags)
+    lib = L.load()
+    if qbuf is None:
+        return lib.b200_seq_merge_peers(pa, fa, n, me, epoch, R, D, L.ptr(gate), L.ptr(out), _stream(s)) == L.OK
+    return lib.b200_seq_merge_peers_a16(pa, fa, n, me, epoch, R, D, L.ptr(gate), L.ptr(out), L.ptr(qbuf), _stream(s)) == L.OK
+
+
 def attn_prefill(q, c, out, T, p0, Hq, scale, s=None):
     return L.load().b200_attn_prefill(L.ptr(q), C.byref(c.c()), L.ptr(out), T, p0, Hq, scale, _stream(s)) == L.OK
 

@@ -71,6 +71,12 @@ SIGNATURES = {
     "b200_attn_merge_gate": (I, [P, P, P, I, I, I, P, P, P]),
     "b200_seq_exchange_merge": (I, [P, I, P, P, I, I, P, P, P]),
     "b200_seq_exchange_merge_a16": (I, [P, I, P, P, I, I, P, P, P, P]),
+    "b200_peer_alloc": (I, [SZ, P, P]),
+    "b200_peer_open": (I, [P, P]),
+    "b200_peer_close": (I, [P]),
+    "b200_peer_free": (I, [P]),
+    "b200_seq_merge_peers": (I, [P, P, I, I, U32, I, I, P, P, P]),
+    "b200_seq_merge_peers_a16": (I, [P, P, I, I, U32, I, I, P, P, P, P]),
     "b200_attn_chunk_keys": (I, []),
     "b200_attn_prefill": (I, [P, KVP, P, I, I, I, F, P]),
     "b200_attn_prefill_variant": (I, [P, KVP, P, I, I, I, F, P, I]),

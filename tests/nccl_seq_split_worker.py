@@ -1,5 +1,6 @@
 """Worker of tests/test_gpu_misc.py::test_two_gpu_sequence_split_nccl: two GPUs hold alternate pages of every slot, compute
-partial (O, m, l) with the library, all-gather them over NCCL and merge; rank results must equal the oracle."""
+partial (O, m, l) with the library, all-gather them over NCCL and merge; rank results must equal the oracle; then the same
+merge over peer-mapped buffers (no collective) must give the same bits."""
 import os
 
 import numpy as np
@@ -79,6 +80,22 @@ def main():
     assert torch.equal(out, out2), "C exchange differs from the torch.distributed exchange"
     nccl.ncclCommDestroy.argtypes = [C.c_void_p]
     nccl.ncclCommDestroy(comm)
+    # the same merge without a collective: partials read in place over peer-mapped buffers, three calls in a row (the two
+    # buffers alternate; the second call sees other queries, so a stale read of the first would show)
+    pm_ = Dm.PeerMerge(plan, rows, hq, 256, dev, None)
+    for call in range(3):
+        qq = q if call != 1 else q[::-1].copy()
+        a_o, a_m, a_l = pm_.views()
+        assert fast.attn_decode_slots_partial(util.to_dev(qq, dev), c, a_o, a_m, a_l, len(lens), q_len, util.to_dev(lpos, dev), 2049, hq,
+                                              util.SCALE)
+        out3 = torch.zeros_like(out)
+        pm_.exchange_and_merge(util.to_dev(gate, dev), out3)
+        torch.cuda.synchronize()
+        assert fast.device_status() == 0
+        if call != 1:
+            assert torch.equal(out, out3), "peer-mapped merge differs from the NCCL exchange (call %d)" % call
+        else:
+            assert not torch.equal(out, out3)
     dist.barrier()
     dist.destroy_process_group()
     print("OK rank", rank)
