@@ -749,17 +749,19 @@ decode_part_k(const dec_args a, const int nslot, const __grid_constant__ CUtenso
     }
 }
 
-// Merge a row's chunk partials.  grid (rows, Hq), 256 threads = 4 groups of 64 (one float4 of the head each): group w sums the
-// chunks w, w + 4, .. in ascending order, the four group sums are added in group order: a fixed order for a given number of
-// chunks, so a row's result does not depend on the rest of the call.
+// Merge a row's chunk partials.  grid (rows, Hq), MERGE_GROUPS groups of 64 threads (one float4 of the head each): group w
+// sums the chunks w, w + G, .. in ascending order, the group sums are added in group order: a fixed order for a given number
+// of chunks, so a row's result does not depend on the rest of the call (the fixed-chunk modes run four groups).
 //   out != nullptr : out = num / den (* sigmoid(gate)); rows that saw no key give zeros
 //   fo  != nullptr : unnormalised num, max in natural-log units, den (for a cross-GPU merge)
-constexpr int MERGE_GROUPS = 4;
+// The even split leaves one to a few partials per row (one per CTA run that crosses the slot): there one group of 64 threads
+// per (row, head) keeps the launch to little more than one wave of small blocks.
+template <int MERGE_GROUPS>
 __global__ void __launch_bounds__(64 * MERGE_GROUPS) decode_merge_k(const dec_args a, const float * __restrict__ gate, float * __restrict__ out,
                                                      float * __restrict__ fo, float * __restrict__ fm, float * __restrict__ fl,
                                                      __half2 * __restrict__ qbuf) {
-    __shared__ float4 gnum[MERGE_GROUPS - 1][64];
-    __shared__ float gden[MERGE_GROUPS - 1];
+    __shared__ float4 gnum[MERGE_GROUPS > 1 ? MERGE_GROUPS - 1 : 1][64];
+    __shared__ float gden[MERGE_GROUPS > 1 ? MERGE_GROUPS - 1 : 1];
     const int lane4 = threadIdx.x & 63, grp = threadIdx.x >> 6;
     const int h = blockIdx.y, row = blockIdx.x, slot = row / a.q_len, j = row - slot * a.q_len;
     const int hk = h / GQA, hh = h - hk * GQA, r = j * GQA + hh, R = a.q_len * GQA;
@@ -788,17 +790,19 @@ __global__ void __launch_bounds__(64 * MERGE_GROUPS) decode_merge_k(const dec_ar
         const float4 o = reinterpret_cast<const float4 *>(a.po + (u * R + r) * DH)[lane4];
         num.x = fmaf(f, o.x, num.x); num.y = fmaf(f, o.y, num.y); num.z = fmaf(f, o.z, num.z); num.w = fmaf(f, o.w, num.w);
     }
-    if (grp > 0) {
-        gnum[grp - 1][lane4] = num;
-        if (lane4 == 0) gden[grp - 1] = den;
-    }
-    __syncthreads();
-    if (grp > 0) return;
+    if constexpr (MERGE_GROUPS > 1) {
+        if (grp > 0) {
+            gnum[grp - 1][lane4] = num;
+            if (lane4 == 0) gden[grp - 1] = den;
+        }
+        __syncthreads();
+        if (grp > 0) return;
 #pragma unroll
-    for (int w = 0; w < MERGE_GROUPS - 1; ++w) {
-        const float4 o = gnum[w][lane4];
-        num.x += o.x; num.y += o.y; num.z += o.z; num.w += o.w;
-        den += gden[w];
+        for (int w = 0; w < MERGE_GROUPS - 1; ++w) {
+            const float4 o = gnum[w][lane4];
+            num.x += o.x; num.y += o.y; num.z += o.z; num.w += o.w;
+            den += gden[w];
+        }
     }
     const size_t oi = ((size_t) row * a.Hq + h) * (DH / 4) + lane4;
     if (fo) {   // public partials are plain sums: take the internal 2^PSHIFT out (exact)
@@ -1405,7 +1409,8 @@ int decode_launch(const float * q, const b200_kv_cache * c, const merge_out & mo
     else if (c->type == B200_KV_Q8_0) rc = launch_part_nt<B200_KV_Q8_0>(a, blocks, s);
     else rc = launch_part_nt<B200_KV_Q4_0>(a, blocks, s);
     if (rc != B200_OK) return rc;
-    decode_merge_k<<<dim3(n_slots * q_len, Hq), 64 * MERGE_GROUPS, 0, s>>>(a, mo.gate, mo.out, mo.fo, mo.fm, mo.fl, (__half2 *) mo.qbuf);
+    if (gm.split) decode_merge_k<1><<<dim3(n_slots * q_len, Hq), 64, 0, s>>>(a, mo.gate, mo.out, mo.fo, mo.fm, mo.fl, (__half2 *) mo.qbuf);
+    else decode_merge_k<4><<<dim3(n_slots * q_len, Hq), 256, 0, s>>>(a, mo.gate, mo.out, mo.fo, mo.fm, mo.fl, (__half2 *) mo.qbuf);
     count_launch(launches);
     return launch_status(who);
 }
