@@ -306,15 +306,9 @@ decode_tc_k(const dec_args a, const __grid_constant__ CUtensorMap mapK, const __
                         uint32_t r[16];
                         const uint32_t sc = valid ? *reinterpret_cast<const uint16_t *>(row + 2 * (vb + 4 * u)) : 0u;
                         tc_block(row, vb + 4 * u, __byte_perm(sc, sc, 0x1010), r);
-#ifdef TC_V_SCALAR
-#pragma unroll
-                        for (int c = 0; c < 16; ++c)
-                            *reinterpret_cast<volatile uint32_t *>(vdst + u * 2048 + (c >> 2) * 128 + (c & 3) * 4) = r[c];
-#else
 #pragma unroll
                         for (int c = 0; c < 4; ++c)
                             *reinterpret_cast<uint4 *>(vdst + u * 2048 + c * 128) = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
-#endif
                     }
                 }
                 if (i + 1 < nt) k_publish(G + 1);
