@@ -65,4 +65,11 @@ def test_refusals_without_launch(lib):
     assert lib.b200_kv_append(C.byref(c), None, None, 0, 1, None) == L.ERR_SHAPE
     assert lib.b200_attn_decode(None, C.byref(c), None, 1, 0, 24, 0.0625, None) == L.ERR_SHAPE
     assert lib.b200_attn_decode_rows(None, C.byref(c), None, 1, None, 24, 0.0625, None) == L.ERR_SHAPE
+    # the peer merge: null tables, more shards than the kernel takes, a shard index outside the group
+    two = (C.c_void_p * 2)(0, 0)
+    assert lib.b200_seq_merge_peers(None, None, 2, 0, 1, 24, 256, None, None, None) == L.ERR_SHAPE
+    assert lib.b200_seq_merge_peers(two, two, 9, 0, 1, 24, 256, None, C.c_void_p(16), None) == L.ERR_SHAPE
+    assert lib.b200_seq_merge_peers(two, two, 2, 2, 1, 24, 256, None, C.c_void_p(16), None) == L.ERR_SHAPE
+    assert lib.b200_seq_merge_peers(two, two, 2, 0, 1, 24, 256, None, C.c_void_p(16), None) == L.ERR_SHAPE   # unmapped shards
+    assert lib.b200_peer_open(None, None) == L.ERR_SHAPE and lib.b200_peer_alloc(0, None, None) == L.ERR_SHAPE
     assert lib.b200_launch_count() == n0

@@ -164,6 +164,47 @@ def test_two_gpu_sequence_split_nccl(cuda, lib):
     assert r.returncode == 0 and r.stdout.count("OK") == 2, r.stdout + r.stderr
 
 
+def test_peer_merge_on_one_gpu_and_a_wait_that_runs_out(cuda, lib):
+    """the peer merge with both "shards" on one GPU: the peer's flag row is written by hand, so the kernel's wait finds
+    it set and the merge equals attn_merge_gate over the two parts; then a call whose announcement never comes: the wait
+    gives up after its limit, the status word says so, and the context stays usable"""
+    import time
+    import torch
+    from p100e_engine_b200 import fast
+    R, Dm = 24, 256
+    rng = np.random.default_rng(6)
+    part_floats = R * (Dm + 2)
+    # one buffer per shard: [partial | flag row of 64 words]
+    bufs = [torch.zeros(part_floats + 64, device=cuda) for _ in range(2)]
+    po = torch.from_numpy(rng.standard_normal((2, R, Dm)).astype(np.float32)).to(cuda)
+    pm = torch.from_numpy(rng.standard_normal((2, R)).astype(np.float32)).to(cuda)
+    pl = torch.from_numpy((rng.random((2, R)) + 0.5).astype(np.float32)).to(cuda)
+    for s in range(2):
+        bufs[s][:part_floats] = torch.cat([po[s].reshape(-1), pm[s], pl[s]])
+    gate = torch.from_numpy(rng.standard_normal((R, Dm)).astype(np.float32)).to(cuda)
+    parts = [b.data_ptr() for b in bufs]
+    flags = [b.data_ptr() + 4 * part_floats for b in bufs]
+    want = torch.zeros(R, Dm, device=cuda)
+    assert fast.attn_merge_gate(po, pm, pl, 2, R, Dm, gate, want)
+    # shard 0's view: shard 1 has announced call 1 (word 1 of shard 0's flag row)
+    bufs[0][part_floats:].view(torch.int32)[1] = 1
+    out = torch.zeros(R, Dm, device=cuda)
+    assert fast.seq_merge_peers(parts, flags, 0, 1, R, Dm, gate, out)
+    torch.cuda.synchronize()
+    assert fast.device_status() == 0
+    assert torch.equal(out, want)
+    assert int(bufs[1][part_floats:].view(torch.int32)[0]) == 1   # and shard 0 announced itself in shard 1's row
+    # call 2 is never announced by shard 1
+    t0 = time.time()
+    assert fast.seq_merge_peers(parts, flags, 0, 2, R, Dm, gate, out)
+    torch.cuda.synchronize()
+    assert 1.0 < time.time() - t0 < 30.0
+    assert fast.device_status() & 1
+    assert fast.attn_merge_gate(po, pm, pl, 2, R, Dm, gate, out)   # the context still works
+    torch.cuda.synchronize()
+    assert fast.device_status() == 0 and torch.equal(out, want)
+
+
 def test_seq_exchange_merge_single_shard(cuda, lib):
     """with one sequence shard the exchange entry point needs no communicator: it normalises and gates the flat partial
     exactly as attn_merge_gate does with one part"""
