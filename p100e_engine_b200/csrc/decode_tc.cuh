@@ -140,6 +140,36 @@ decode_tc_k(const dec_args a, const __grid_constant__ CUtensorMap mapK, const __
         const int32_t * tab = a.g.pt ? a.g.pt + (a.g.rtab ? a.g.rtab[slot * a.q_len] : 0) : nullptr;
         const int pg0 = tab ? k_lo >> a.g.psh : 0;
         const int ib = 2 * g;
+        // Staging item q of the run, in the order the workers consume them (K0, K1, V0, K2, V1, .., K(nt-1), V(nt-2), V(nt-1)):
+        // one or two 64-position boxes (boxes past the run's end hold no key) into ring buffer (2 g + q) mod 4.  Called by the
+        // whole TMA warp with warp-uniform arguments; the elected lane issues.  staged: page entries come from shared memory.
+        auto issue_item = [&](int q, bool lead, bool staged) {
+            const bool is_v = q == 2 * nt - 1 || (q > 0 && (q & 1) == 0);
+            const int tile = q == 0 ? 0 : q == 2 * nt - 1 ? nt - 1 : is_v ? (q - 2) >> 1 : (q + 1) >> 1;
+            const int p_t = k_lo + tile * UT;
+            const CUtensorMap * map = is_v ? &mapV : &mapK;
+            const int nbox = p_t + TILE < k_hi ? 2 : 1;
+            const int buf = (ib + q) & (TC_NBUF - 1);
+            unsigned char * dst = stg + (size_t) buf * BUF;
+            if (lead) mbar_expect_tx(&full[buf], (uint32_t) nbox * TILE * HB);
+            for (int h = 0; h < nbox; ++h) {
+                const int p = p_t + h * TILE;
+                int y = p, z = 0;
+                if (tab) {
+                    const int idx = (p >> a.g.psh) - pg0;
+                    z = staged && idx < TC_PGS ? pgs[idx] : tab[p >> a.g.psh];
+                    y = p & ((1 << a.g.psh) - 1);
+                    if (z < 0) { if (lead) atomicOr(a.status, ST_BAD_PAGE); z = 0; }
+                }
+                if (lead) tma_box3(dst + h * TILE * HB, map, hk * (HB / 2), y, z, &full[buf]);
+            }
+        };
+        // The ring is empty at the start of a run (the previous run's end barrier): its first items go out now, before the
+        // workers stage the page entries and the query rows, so that the copies fly during that prologue.
+        if (w == TC_WORKERS / 32 + 1) {
+            const bool lead = umma::elect_one();
+            for (int q = 0; q < TC_NBUF && q < 2 * nt; ++q) issue_item(q, lead, false);
+        }
         if (worker) {
             if (tab) {
                 const int npg = min(TC_PGS, ((k_hi - 1) >> a.g.psh) - pg0 + 1);
@@ -204,45 +234,14 @@ decode_tc_k(const dec_args a, const __grid_constant__ CUtensorMap mapK, const __
                     }
                 }
             } else {
-                const int klo_u = __shfl_sync(0xffffffffu, k_lo, 0), khi_u = __shfl_sync(0xffffffffu, k_hi, 0);
-                const int pg0_u = __shfl_sync(0xffffffffu, pg0, 0), ib_u = 2 * g_u;
-                for (int q = 0; q < 2 * nt_u; ++q) {   // staging item q of the run, in the order the workers consume them
-                    if (q >= TC_NBUF) {
-                        // its buffer held item q - 4: the K rows of a tile are free once every worker has widened them, the V
-                        // rows once every worker has written its part of the image
-                        const int pq = q - TC_NBUF;
-                        const bool was_v = pq > 0 && (pq & 1) == 0;
-                        const int G = g_u + (pq == 0 ? 0 : was_v ? (pq - 2) >> 1 : (pq + 1) >> 1);
-                        tc_wait(was_v ? &p_ready[G & 1] : &kconv[G & 1], (uint32_t) ((G >> 1) & 1), a.status, 7);
-                    }
-                    // the item's 64-position boxes: (tensor map, row in page, page) of box h; boxes past the run's end hold no key
-                    auto boxes = [&](int item, const CUtensorMap *& map, int & p_t) {
-                        const bool is_v = item == 2 * nt_u - 1 || (item > 0 && (item & 1) == 0);
-                        const int tile = item == 0 ? 0 : item == 2 * nt_u - 1 ? nt_u - 1 : is_v ? (item - 2) >> 1 : (item + 1) >> 1;
-                        p_t = klo_u + tile * UT;
-                        map = is_v ? &mapV : &mapK;
-                        return p_t + TILE < khi_u ? 2 : 1;
-                    };
-                    auto coords = [&](int p, int & y, int & z) {
-                        y = p; z = 0;
-                        if (tab) {
-                            const int idx = (p >> a.g.psh) - pg0_u;
-                            z = idx < TC_PGS ? pgs[idx] : tab[p >> a.g.psh];
-                            y = p & ((1 << a.g.psh) - 1);
-                            if (z < 0) { if (lead) atomicOr(a.status, ST_BAD_PAGE); z = 0; }
-                        }
-                    };
-                    const CUtensorMap * map;
-                    int p_t;
-                    const int nbox = boxes(q, map, p_t);
-                    const int buf = (ib_u + q) & (TC_NBUF - 1);
-                    unsigned char * dst = stg + (size_t) buf * BUF;
-                    if (lead) mbar_expect_tx(&full[buf], (uint32_t) nbox * TILE * HB);
-                    for (int h = 0; h < nbox; ++h) {
-                        int y, z;
-                        coords(p_t + h * TILE, y, z);
-                        if (lead) tma_box3(dst + h * TILE * HB, map, hk * (HB / 2), y, z, &full[buf]);
-                    }
+                for (int q = TC_NBUF; q < 2 * nt_u; ++q) {   // the first TC_NBUF items went out before the prologue
+                    // its buffer held item q - 4: the K rows of a tile are free once every worker has widened them, the V
+                    // rows once every worker has written its part of the image
+                    const int pq = q - TC_NBUF;
+                    const bool was_v = pq > 0 && (pq & 1) == 0;
+                    const int G = g_u + (pq == 0 ? 0 : was_v ? (pq - 2) >> 1 : (pq + 1) >> 1);
+                    tc_wait(was_v ? &p_ready[G & 1] : &kconv[G & 1], (uint32_t) ((G >> 1) & 1), a.status, 7);
+                    issue_item(q, lead, true);
                 }
             }
             __syncwarp();
