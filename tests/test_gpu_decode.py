@@ -297,6 +297,15 @@ def test_even_split_64_row_pages_and_long_page_lists(cuda, lib):
     util.check_close(got, ref, "even split, 64-row pages")
 
 
+def test_even_split_many_short_slots(cuda, lib):
+    """a wide batch of short sequences: every CTA of the tcgen05 kernel walks many one- and two-tile runs, so the staging
+    ring, the tensor-memory buffers and the barrier phases carry over from run to run dozens of times"""
+    rng = np.random.default_rng(31)
+    lens = [int(x) for x in rng.integers(3, 400, size=150)]
+    got, ref, _ = _verify_batch(cuda, TYPES["q8_0"], len(lens), 3, lens, 29, -1)
+    util.check_close(got, ref, "even split, 150 short slots")
+
+
 def test_even_split_contiguous_cache_several_row_groups(cuda, lib):
     """the batched entry point on a contiguous cache: three row groups at different depths of one sequence, chosen split"""
     import torch
