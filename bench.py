@@ -453,7 +453,18 @@ class Workload:
         if not ok:
             raise RuntimeError("a library call was refused")
 
+    def begin_step(self):
+        """the rows' positions are those of a model step: the same for every layer (the library then computes the split of
+        the batch once per step and stream instead of once per layer call)"""
+        nbytes = 4 * self.rows
+        if self.merge is None:
+            self.fast.attn_step_begin(self.last_key, nbytes)
+        else:
+            for st in self.sub_streams:
+                self.fast.attn_step_begin(self.last_key, nbytes, st)
+
     def step(self, events=None):
+        self.begin_step()
         for l in range(self.layers):
             self.layer(l, self.d_qg[l], self.d_k[l], self.d_v[l], None if events is None else events[l])
 
@@ -505,6 +516,7 @@ class Workload:
             self.e2e_setup()
         self.h2d_stream.wait_stream(main)
         self.d2h_stream.wait_stream(main)
+        self.begin_step()
         r = self.plan.seq_rank
         a, b_ = self.my
         for l in range(self.layers):
@@ -554,6 +566,7 @@ class Workload:
         for it in range(steps + 1):
             ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)] for _ in range(self.layers)]
             torch.cuda.synchronize()
+            fast.attn_step_begin(self.last_key, 4 * self.rows)
             t0 = time.perf_counter()
             for l in range(self.layers):
                 c = self.caches[l]

@@ -148,6 +148,15 @@ int b200_attn_fixed_chunk(int n_ctx);  /* the chunk the entry points above use f
  * kernel.  set_tc(0) keeps the mma.sync kernel everywhere, set_tc(1) restores the default, set_tc(-1) re-reads
  * B200ATTN_TC (0 = off); tc() reports the setting.  Both kernels meet the same tolerance; their results are not bitwise
  * equal. */
+/* A model step does not change the rows' positions from layer to layer, and the even split of a batch (chunk_keys = -1)
+ * depends on nothing else.  b200_attn_step_begin(stream, positions, bytes) declares that the device array `positions`
+ * (`bytes` long) stays as it is until the next step_begin / step_end on that stream.  Until then the batched entry points
+ * called on the stream with a `pos` argument inside that array reuse the split that the first call of a given shape (position
+ * pointer, slots, q_len, max_n, cache geometry) left in the stream's scratch instead of recomputing it per call; any call
+ * of another shape on the stream drops it.  Without step_begin every call computes its own split.  b200_pool_step
+ * declares its step descriptor this way on its stream, b200_pool_destroy ends the step. */
+int b200_attn_step_begin(void *stream, const int32_t *positions, size_t bytes);
+int b200_attn_step_end(void *stream);
 int b200_attn_dec_tc(void);
 void b200_attn_dec_set_tc(int on);
 

@@ -1108,12 +1108,32 @@ int fixed_chunk(int n_ctx) {
 // fit neither allocate nor synchronise, and the pointer does not move (recorded work stays valid).  A call that needs more
 // gets a new, larger buffer; the old one is kept allocated until the process exits, so nothing that was recorded against
 // it ever reads freed memory, and no stream is synchronised.
-struct scratch { int dev = -1; cudaStream_t s = nullptr; float * p = nullptr; size_t cap = 0; };
+// The even split of a batch depends on the rows' positions only, which a model step does not change from layer to layer.
+// Between b200_attn_step_begin(stream, positions, bytes) and the next one (or b200_attn_step_end) the plan that the first
+// batched call of a given shape, with its positions inside the declared array, leaves in the stream's scratch is used again by
+// the following calls of the same shape instead of being recomputed: what identifies the plan is kept here, and any other
+// call on the stream drops it.
+struct plan_key {
+    const void * scr = nullptr, * pos = nullptr, * p0p = nullptr;
+    int p0 = 0, n_slots = 0, q_len = 0, max_chunks = 0, max_cta = 0, Hkv = 0, n_ctx = 0, paged = 0;
+    size_t part_floats = 0;
+    bool operator==(const plan_key & o) const {
+        return scr == o.scr && pos == o.pos && p0p == o.p0p && p0 == o.p0 && n_slots == o.n_slots && q_len == o.q_len &&
+               max_chunks == o.max_chunks && max_cta == o.max_cta && Hkv == o.Hkv && n_ctx == o.n_ctx && paged == o.paged &&
+               part_floats == o.part_floats;
+    }
+};
+struct scratch {
+    int dev = -1; cudaStream_t s = nullptr; float * p = nullptr; size_t cap = 0;
+    bool step_mode = false, plan_valid = false;
+    const char * step_lo = nullptr, * step_hi = nullptr;   // the position array the caller declared fixed for the step
+    plan_key key;
+};
 scratch g_scr[64];
 int g_nscr = 0;
 std::mutex g_mu;
 
-float * scratch_for(cudaStream_t s, size_t floats, size_t floats_hint) {
+scratch * scratch_entry(cudaStream_t s, size_t floats, size_t floats_hint) {
     int dev = 0;
     cudaGetDevice(&dev);
     std::lock_guard<std::mutex> lk(g_mu);
@@ -1130,8 +1150,13 @@ float * scratch_for(cudaStream_t s, size_t floats, size_t floats_hint) {
         if (cudaMalloc(&p, want * sizeof(float)) != cudaSuccess) { cudaGetLastError(); return nullptr; }
         e->p = p;      // the previous buffer, if any, stays allocated (see above)
         e->cap = want;
+        e->plan_valid = false;
     }
-    return e->p;
+    return e;
+}
+float * scratch_for(cudaStream_t s, size_t floats, size_t floats_hint) {
+    scratch * e = scratch_entry(s, floats, floats_hint);
+    return e ? e->p : nullptr;
 }
 
 // ---- tensor maps of the cache ----------------------------------------------------------------------------------
@@ -1372,7 +1397,7 @@ struct merge_out { float * out; const float * gate; float * fo, * fm, * fl; void
 // the kernels of one call, partials and work list in `scr`
 int decode_launch(const float * q, const b200_kv_cache * c, const merge_out & mo, int n_slots, int q_len, const int32_t * pos,
                   const int32_t * p0p, int p0, int Hq, float scale, const dec_geom & gm, float * scr, unsigned * st, cudaStream_t s,
-                  const char * who) {
+                  const char * who, bool reuse_plan = false) {
     dec_args a;
     a.q = q; a.g = view_of(*c);
     a.po = scr; a.pm = scr + gm.units * gm.R * DH; a.pl = a.pm + gm.units * gm.R;
@@ -1393,8 +1418,10 @@ int decode_launch(const float * q, const b200_kv_cache * c, const merge_out & mo
         int * cta_seg = list + 4 * nseg + 2 * (size_t) n_slots;
         int * n_cta = cta_seg + gm.max_cta + 1;
         a.segs = segs; a.cta_seg = cta_seg; a.slot_seg = slot_seg; a.n_cta = n_cta;
-        decode_split_k<<<1, SPLIT_THR, 0, s>>>(a, gm.max_cta, segs, cta_seg, slot_seg, n_cta);
-        ++launches;
+        if (!reuse_plan) {   // else the lists of an earlier call of this step, same shape, same positions, are still there
+            decode_split_k<<<1, SPLIT_THR, 0, s>>>(a, gm.max_cta, segs, cta_seg, slot_seg, n_cta);
+            ++launches;
+        }
         blocks = (unsigned) gm.max_cta * (unsigned) c->Hkv;
     } else if (gm.planned) {
         int * list = reinterpret_cast<int *>(scr + gm.part_floats);
@@ -1428,11 +1455,20 @@ int decode_impl(const float * q, const b200_kv_cache * c, const merge_out & mo, 
     dec_geom gm;
     if (!decode_geometry(gm, c->type, n_slots, q_len, max_n, c->n_ctx, c->Hkv, chunk_keys, tc_eligible(*c, q_len))) B200_REFUSE(B200_ERR_SHAPE, "%s: too many chunks", who);
     const size_t need = gm.part_floats + gm.list_ints;
-    float * scr = scratch_for(s, need, hint_floats);
-    if (!scr) B200_REFUSE(B200_ERR_ALLOC, "%s: split scratch (%zu floats) could not be allocated", who, need);
+    scratch * e = scratch_entry(s, need, hint_floats);
+    if (!e || !e->p) B200_REFUSE(B200_ERR_ALLOC, "%s: split scratch (%zu floats) could not be allocated", who, need);
+    float * scr = e->p;
     unsigned * st = device_status_word();
     if (!st) return B200_ERR_CUDA;
-    return decode_launch(q, c, mo, n_slots, q_len, pos, p0p, p0, Hq, scale, gm, scr, st, s, who);
+    plan_key k;
+    k.scr = scr; k.pos = pos; k.p0p = p0p; k.p0 = p0; k.n_slots = n_slots; k.q_len = q_len; k.max_chunks = gm.max_chunks;
+    k.max_cta = gm.max_cta; k.Hkv = c->Hkv; k.n_ctx = c->n_ctx; k.paged = c->pt != nullptr; k.part_floats = gm.part_floats;
+    const bool in_step = e->step_mode && pos && (const char *) pos >= e->step_lo && (const char *) pos < e->step_hi;
+    const bool reuse = gm.split && in_step && e->plan_valid && k == e->key;
+    const int rc = decode_launch(q, c, mo, n_slots, q_len, pos, p0p, p0, Hq, scale, gm, scr, st, s, who, reuse);
+    e->plan_valid = gm.split && in_step && rc == B200_OK;   // any other call on the stream rewrites the scratch
+    e->key = k;
+    return rc;
 }
 
 // ---- decode / verify without any allocation --------------------------------------------------------------------
@@ -1523,6 +1559,24 @@ int b200_attn_dec2_nsplit(int Hkv) {
     return g_nsplit_override > 0 ? g_nsplit_override : MAX_DEFAULT_CHUNKS;
 }
 void b200_attn_dec2_set_nsplit(int n) { g_nsplit_override = n > 0 ? n : 0; }
+int b200_attn_step_begin(void * stream, const int32_t * positions, size_t bytes) {
+    if (!positions || !bytes) B200_REFUSE(B200_ERR_SHAPE, "attn_step_begin: null position array");
+    scratch * e = scratch_entry((cudaStream_t) stream, 0, 0);
+    if (!e) B200_REFUSE(B200_ERR_ALLOC, "attn_step_begin: too many (device, stream) pairs");
+    e->step_mode = true;
+    e->plan_valid = false;
+    e->step_lo = (const char *) positions;
+    e->step_hi = e->step_lo + bytes;
+    return B200_OK;
+}
+int b200_attn_step_end(void * stream) {
+    scratch * e = scratch_entry((cudaStream_t) stream, 0, 0);
+    if (!e) return B200_OK;
+    e->step_mode = false;
+    e->plan_valid = false;
+    e->step_lo = e->step_hi = nullptr;
+    return B200_OK;
+}
 int b200_attn_dec_tc(void) { return tc_enabled() ? 1 : 0; }
 void b200_attn_dec_set_tc(int on) { g_tc = on < 0 ? -1 : on ? 1 : 0; }
 int b200_attn_dec2_reload_env(void) {

@@ -30,6 +30,8 @@ struct b200_pool {
     std::vector<int32_t> n_alloc;
     // step descriptor: [pos_g | pos_l | crow | rtab] x max_rows, two pinned staging buffers used in turn
     int max_rows, rows, max_n, turn;
+    void * step_stream = nullptr;   // the stream of the last step (whose attention calls share one split plan)
+    bool stepped = false;
     int32_t * step_h[2], * step_d;
     cudaEvent_t step_ev[2];
     bool ev_used[2];
@@ -159,6 +161,7 @@ void b200_pool_destroy(b200_pool * p) {
     if (!p) return;
     if (on_device(p)) {
         cudaSetDevice(p->dev);
+        if (p->stepped) b200_attn_step_end(p->step_stream);   // its step descriptor is about to go away
         if (p->base) cudaFree(p->base);
         if (p->ptab_d) cudaFree(p->ptab_d);
         if (p->ptab_h) cudaFreeHost(p->ptab_h);
@@ -280,6 +283,11 @@ int b200_pool_step(b200_pool * p, const int32_t * slots, const int32_t * n_past,
         cudaEventRecord(p->step_ev[turn], s);
         p->ev_used[turn] = true;
         p->turn ^= 1;
+        // the positions of this step are now fixed: the batched attention calls on this stream may share one split plan
+        const int rc = b200_attn_step_begin(stream, p->step_d, 4 * (size_t) mr * sizeof(int32_t));
+        if (rc != B200_OK) return rc;
+        p->step_stream = stream;
+        p->stepped = true;
     }
     return B200_OK;
 }

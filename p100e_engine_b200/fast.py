@@ -129,6 +129,18 @@ def seq_exchange_merge_a16(nccl_comm, n_seq, send, recv, R, D, gate, out, qbuf, 
                                                 L.ptr(out), L.ptr(qbuf), _stream(s)) == L.OK
 
 
+def attn_step_begin(positions, nbytes=None, s=None):
+    """the device array `positions` stays as it is until the next call: batched calls on the stream whose pos argument lies
+    inside it reuse the even split within the step"""
+    if nbytes is None:
+        nbytes = positions.numel() * positions.element_size()
+    return L.load().b200_attn_step_begin(_stream(s), L.ptr(positions), nbytes) == L.OK
+
+
+def attn_step_end(s=None):
+    return L.load().b200_attn_step_end(_stream(s)) == L.OK
+
+
 def peer_alloc(nbytes):
     """(device address, 64-byte handle) of a zero-filled buffer that other processes of the node can map"""
     p, h = C.c_void_p(), (C.c_ubyte * 64)()

@@ -58,6 +58,8 @@ SIGNATURES = {
     "b200_attn_decode2": (I, [P, KVP, P, I, I, P, I, F, P, P]),
     "b200_attn_dec2_nsplit": (I, [I]),
     "b200_attn_dec2_set_nsplit": (None, [I]),
+    "b200_attn_step_begin": (I, [P, P, SZ]),
+    "b200_attn_step_end": (I, [P]),
     "b200_attn_dec_tc": (I, []),
     "b200_attn_dec_set_tc": (None, [I]),
     "b200_attn_dec2_reload_env": (I, []),

@@ -306,6 +306,44 @@ def test_even_split_many_short_slots(cuda, lib):
     util.check_close(got, ref, "even split, 150 short slots")
 
 
+def test_split_plan_is_shared_inside_a_declared_step(cuda, lib):
+    """between attn_step_begin(positions) and step_end the batched calls of one shape launch the split kernel once; the
+    results are the same bits; a call of another shape, a position array outside the declared one, or step_end bring
+    the per-call split back"""
+    import torch
+    from p100e_engine_b200 import fast
+    lens = [1500, 300, 2049, 77, 900]
+    q_len = 4
+    got, ref, (q, gate, pos, rtab, c, pool, pool_t, pt_t) = _verify_batch(cuda, TYPES["q8_0"], len(lens), q_len, lens, 41, -1)
+    util.check_close(got, ref, "reference call")
+    qd, gd, pos_t = util.to_dev(q, cuda), util.to_dev(gate, cuda), util.to_dev(pos, cuda)
+    out = torch.zeros(len(lens) * q_len, HQ, D, device=cuda)
+
+    def call(p=pos_t, ql=q_len, n=len(lens)):
+        n0 = lib.b200_launch_count()
+        assert fast.attn_decode_slots(qd[:n * ql], c, out[:n * ql], gd[:n * ql], n, ql, p, max(lens), HQ, SCALE, -1)
+        torch.cuda.synchronize()
+        assert fast.device_status() == 0
+        return lib.b200_launch_count() - n0
+
+    assert call() == 3                        # no step declared: split + attention + merge
+    assert fast.attn_step_begin(pos_t)
+    try:
+        assert call() == 3 and np.array_equal(out.cpu().numpy(), got)
+        assert call() == 2 and np.array_equal(out.cpu().numpy(), got)      # the split of the first call serves the second
+        assert call() == 2
+        other = pos_t.clone()
+        assert call(other) == 3               # positions outside the declared array
+        assert call() == 3                    # that call took the scratch: the plan is computed again ...
+        assert call() == 2                    # ... and shared from then on
+        assert fast.attn_step_begin(pos_t)    # a new step
+        assert call() == 3 and call() == 2
+    finally:
+        assert fast.attn_step_end()
+    assert call() == 3
+    assert np.array_equal(out.cpu().numpy(), got)
+
+
 def test_even_split_contiguous_cache_several_row_groups(cuda, lib):
     """the batched entry point on a contiguous cache: three row groups at different depths of one sequence, chosen split"""
     import torch
