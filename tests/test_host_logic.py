@@ -190,3 +190,22 @@ def test_two_rank_sequence_split_merge_gloo():
     for p, o in zip(procs, outs):
         assert p.returncode == 0, o
         assert "OK" in o, o
+
+
+def _run_peer_workers(fail_rank, port):
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), PYTHONPATH=ROOT)
+    procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "gloo_peer_merge_worker.py"), str(r), "2", str(fail_rank)],
+                              env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=240)[0] for p in procs]
+    for p, o in zip(procs, outs):
+        assert p.returncode == 0, o
+    return outs
+
+
+def test_peer_merge_host_protocol_gloo():
+    """two CPU ranks (gloo), device calls recorded instead of made: the shards map each other's buffers in shard order,
+    alternate the two partial buffers, count the calls alike; when one shard cannot map its peer, both give up"""
+    for o in _run_peer_workers(-1, 29518):
+        assert "OK" in o, o
+    for o in _run_peer_workers(1, 29519):
+        assert "REFUSED" in o, o
