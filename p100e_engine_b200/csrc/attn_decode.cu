@@ -20,6 +20,12 @@
 // The chunk grid is fixed by absolute key index, and a chunk's arithmetic never depends on the other rows of the call:
 // a row's result is a function of its own keys and of chunk_keys only (row t of a T-row call == the 1-row call).
 //
+// Batched calls that let the library choose the split (chunk_keys < 0) cut the batch evenly over the CTAs that fit the GPU
+// (decode_split_k; one plan per model step when the caller declares the step, b200_attn_step_begin).  There q8_0 caches
+// with two to four rows per slot run on a second kernel, decode_tc_k (decode_tc.cuh): tcgen05 MMAs with K in tensor
+// memory and V as an f16 image in shared memory, one CTA per SM.  Everything else, and every fixed-chunk call, runs on
+// the kernel described above.
+//
 // Reference counterpart: dec2_k / attn_decode2 (src/fast/attn_dec2.cu:210-530), fp32 FFMA on sm_60.
 #include "umma.cuh"
 
